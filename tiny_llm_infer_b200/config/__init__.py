@@ -3,3 +3,4 @@ from .base import (ConfigError, ModelConfig, architecture_of, config_from_dict, 
 from .kaketar import KaketarConfig
 from .panolorn import PanolornConfig
 from .qwen3 import Qwen3Config
+from .tetodra import TetodraConfig

@@ -30,7 +30,15 @@ namespace tllm {
 struct ScoreMod {
     float scale, softcap;
     int chunk, window, sink;
+    const float* dist_bias;      // [query heads][dist_len] float32 added to the score by distance, or null
+    int dist_len;                // distances from dist_len - 1 on share the last entry
 };
+
+// The learned bias of a head for a key `dist` tokens back (0 without a table).
+__device__ __forceinline__ float dist_bias_of(const ScoreMod& m, int head, int dist) {
+    if (m.dist_bias == nullptr) return 0.0f;
+    return m.dist_bias[(size_t)head * m.dist_len + min(max(dist, 0), m.dist_len - 1)];
+}
 
 static inline int page_shift_of(int page_size) {
     int shift = 0;
@@ -59,7 +67,9 @@ __global__ void qkv_unit_store_kernel(const T* proj, int row_stride, const T* __
                                       const int* __restrict__ positions, const int* __restrict__ token_slot,
                                       const int* __restrict__ block_table, int max_pages, int page_size,
                                       T* k_plane, T* v_plane, long long page_stride, T* q_out,
-                                      int q_heads, int kv_heads, int dk, int dv, int store) {
+                                      int q_heads, int kv_heads, int dk, int dv, int store,
+                                      const float* __restrict__ inv_freq, int rot_dims, float temp_coef,
+                                      int temp_every, int v_from_k) {
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const int slot = token_slot[t];
@@ -92,14 +102,27 @@ __global__ void qkv_unit_store_kernel(const T* proj, int row_stride, const T* __
             if (is_q) dst = q_out + ((size_t)t * q_heads + head) * dk;
             else if (store) dst = k_plane + page_base + ((size_t)(head - q_heads) * page_size + in_page) * dk;
             else continue;
+            // a query's temperature grows with the logarithm of its position counted in runs of temp_every
+            const float temp = (is_q && temp_every > 0) ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
+            const int half = rot_dims >> 1;
             for (int e = lane; e < dk; e += 32) {
                 float x = to_f32<T>(src[e]) * sc;
                 if (gain != nullptr && do_norm) x *= to_f32<T>(gain[e]);
-                dst[e] = from_f32<T>(x);
+                if (e < rot_dims) {               // element e turns with its partner half a rotated width away
+                    const int partner = e < half ? e + half : e - half;
+                    float y = to_f32<T>(src[partner]) * sc;
+                    if (gain != nullptr && do_norm) y *= to_f32<T>(gain[partner]);
+                    const float ang = (float)pos * inv_freq[e < half ? e : e - half];
+                    const float c = cosf(ang), sn = sinf(ang);
+                    x = e < half ? x * c - y * sn : x * c + y * sn;
+                }
+                dst[e] = from_f32<T>(x * temp);
             }
         } else if (store) {
             const int g = head - q_heads - kv_heads;
-            const T* src = row + (size_t)(q_heads + kv_heads) * dk + (size_t)g * dv;
+            // values of their own, or the keys as they were projected (before their norm)
+            const T* src = v_from_k ? row + (size_t)(q_heads + g) * dk
+                                    : row + (size_t)(q_heads + kv_heads) * dk + (size_t)g * dv;
             T* dst = v_plane + page_base + ((size_t)g * page_size + in_page) * dv;
             for (int e = lane; e < dv; e += 32) dst[e] = src[e];
         }
@@ -160,7 +183,7 @@ __global__ void attention_biased_general_kernel(
             if (e < dk) dot += qs[e] * to_f32<T>(kp[e]);
         }
         dot = warp_sum(dot);
-        const float s = mod_score(dot, slope, pos - j, mod);
+        const float s = mod_score(dot, slope, pos - j, mod) + dist_bias_of(mod, head, pos - j);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);
         const float p = expf(s - m_new);
@@ -397,6 +420,26 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
                     s[nt][e] = mod_score_fast(s[nt][e], slope2, d_lo - back, mod, inv_cap);
                     s[nt][2 + e] = mod_score_fast(s[nt][2 + e], slope2, d_hi - back, mod, inv_cap);
                 }
+            if (mod.dist_bias != nullptr) {
+                // a tile that lies beyond the table for every row of the warp gets the table's last entry;
+                // only the few tiles near the diagonal look distances up one by one
+                const float* tb = mod.dist_bias + (size_t)head * mod.dist_len;
+                const int lastd = mod.dist_len - 1;
+                if (first_pos + warp * 16 - (key0 + kPfN - 1) >= lastd) {
+                    const float far = tb[lastd] * kLog2e;
+#pragma unroll
+                    for (int nt = 0; nt < kPfN / 8; ++nt) { s[nt][0] += far; s[nt][1] += far; s[nt][2] += far; s[nt][3] += far; }
+                } else {
+                    const int n_lo = p_lo - key_base, n_hi = p_hi - key_base;
+#pragma unroll
+                    for (int nt = 0; nt < kPfN / 8; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            s[nt][e] += tb[min(max(n_lo - (nt * 8 + e), 0), lastd)] * kLog2e;
+                            s[nt][2 + e] += tb[min(max(n_hi - (nt * 8 + e), 0), lastd)] * kLog2e;
+                        }
+                }
+            }
             if (!inner) {
 #pragma unroll
                 for (int nt = 0; nt < kPfN / 8; ++nt)
@@ -650,8 +693,12 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
                     const int j = key_base + nt * 8 + e;
                     const bool seen = j <= pos && j >= lo;
                     const float dist = d0 - (float)(nt * 8 + e);
-                    const float a = mod_score_fast(s[nt][e], slope_lo, dist, mod, inv_cap);
-                    const float b = mod_score_fast(s[nt][2 + e], slope_hi, dist, mod, inv_cap);
+                    float a = mod_score_fast(s[nt][e], slope_lo, dist, mod, inv_cap);
+                    float b = mod_score_fast(s[nt][2 + e], slope_hi, dist, mod, inv_cap);
+                    if (mod.dist_bias != nullptr) {
+                        a += dist_bias_of(mod, head0 + (v_lo ? r_lo : 0), pos - j) * kLog2e;
+                        b += dist_bias_of(mod, head0 + (v_hi ? r_hi : 0), pos - j) * kLog2e;
+                    }
                     s[nt][e] = (seen && v_lo) ? a : -INFINITY;
                     s[nt][2 + e] = (seen && v_hi) ? b : -INFINITY;
                     tmax_lo = fmaxf(tmax_lo, s[nt][e]);
@@ -812,9 +859,14 @@ int tllm_qkv_unit_store(const void* proj, int row_stride, const void* q_gain, co
                         int do_norm, const int* positions, const int* token_slot, const int* block_table,
                         int max_pages, int page_size, void* k_plane, void* v_plane, long long page_stride,
                         void* q_out, int dtype, int tokens, int q_heads, int kv_heads, int dk, int dv,
-                        int store, cudaStream_t stream) {
+                        int store, const float* inv_freq, int rot_dims, float temp_coef, int temp_every, int v_from_k,
+                        cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && dk > 0 && dv > 0, "qkv_unit_store: bad sizes");
-    TLLM_REQUIRE(row_stride >= (q_heads + kv_heads) * dk + kv_heads * dv, "qkv_unit_store: rows of %d are too short", row_stride);
+    TLLM_REQUIRE(row_stride >= (q_heads + kv_heads) * dk + (v_from_k ? 0 : kv_heads * dv), "qkv_unit_store: rows of %d are too short", row_stride);
+    TLLM_REQUIRE(rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq != nullptr),
+                 "qkv_unit_store: a rotation of %d of %d elements", rot_dims, dk);
+    TLLM_REQUIRE(!v_from_k || dv == dk, "qkv_unit_store: keys of width %d cannot serve as values of width %d", dk, dv);
+    TLLM_REQUIRE(temp_every >= 0, "qkv_unit_store: negative constant");
     TLLM_REQUIRE(!do_norm || eps > 0.0f, "qkv_unit_store: eps must be positive");
     TLLM_REQUIRE(!store || (k_plane && v_plane && block_table && page_size > 0 && max_pages > 0),
                  "qkv_unit_store: no cache to write to");
@@ -826,7 +878,7 @@ int tllm_qkv_unit_store(const void* proj, int row_stride, const void* q_gain, co
     launch_pdl(kPdlQk, qkv_unit_store_kernel<T>, dim3(tokens), dim3(warps * 32), 0, stream, (const T*)proj,   \
                row_stride, (const T*)q_gain, (const T*)k_gain, eps, do_norm, positions, token_slot,           \
                block_table, max_pages, page_size, (T*)k_plane, (T*)v_plane, page_stride, (T*)q_out, q_heads,  \
-               kv_heads, dk, dv, store)
+               kv_heads, dk, dv, store, inv_freq, rot_dims, temp_coef, temp_every, v_from_k)
     if (dtype == kBF16) STORE(bf16);
     else if (dtype == kF32) STORE(float);
     else TLLM_REQUIRE(false, "qkv_unit_store: unknown dtype %d", dtype);
@@ -838,8 +890,9 @@ int tllm_attention_biased_general(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* positions,
     const int* token_slot, const int* block_table, int max_pages, int page_size, int dtype, int tokens,
     int q_heads, int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const float* sink_logit, int v_row, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    const float* slopes, const float* sink_logit, const float* dist_bias, int dist_len, int v_row, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
     if (v_row <= 0) v_row = dv;
+    TLLM_REQUIRE(dist_bias == nullptr || dist_len > 0, "attention_biased: an empty table of biases");
     TLLM_REQUIRE(v_row >= dv, "attention_biased: values of width %d in rows of %d", dv, v_row);
     TLLM_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0,
                  "attention_biased: %d query heads over %d key/value heads", q_heads, kv_heads);
@@ -848,7 +901,7 @@ int tllm_attention_biased_general(
     TLLM_REQUIRE(tokens <= 65535, "attention_biased: %d tokens in one step exceed 65535", tokens);
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased: negative constant");
     if (tokens == 0) return 0;
-    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
+    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len};
     if (dtype == kBF16)
         return launch_general<bf16>(q, k_plane, v_plane, page_stride, positions, token_slot, block_table, max_pages,
                                     page_size, tokens, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, out, stream);
@@ -871,15 +924,16 @@ int tllm_attention_biased_prefill(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* seg_info,
     const int* tiles, int n_tiles, const int* block_table, int max_pages, int page_size, int q_heads,
     int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const float* sink_logit, int v_row, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    const float* slopes, const float* sink_logit, const float* dist_bias, int dist_len, int v_row, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
     if (v_row <= 0) v_row = dv;
+    TLLM_REQUIRE(dist_bias == nullptr || dist_len > 0, "attention_biased_prefill: an empty table of biases");
     TLLM_REQUIRE(v_row >= dv && v_row % 8 == 0, "attention_biased_prefill: values of width %d in rows of %d", dv, v_row);
     TLLM_REQUIRE(tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv), "attention_biased_prefill: sizes %d/%d heads, widths %d/%d", q_heads, kv_heads, dk, dv);
     TLLM_REQUIRE(page_size > 0 && max_pages > 0 && n_tiles >= 0 && q_heads <= 65535, "attention_biased_prefill: bad geometry");
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_prefill: negative constant");
     TLLM_REQUIRE(gate == nullptr || gate_stride % 2 == 0, "attention_biased_prefill: odd gate stride");
     if (n_tiles == 0) return 0;
-    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
+    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len};
 #define PF(A, B) launch_biased_prefill<A, B>(q, k_plane, v_plane, page_stride, seg_info, tiles, n_tiles, block_table, max_pages, \
                                              page_size, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, out, stream)
     if (dk <= 64) return dv <= 64 ? PF(64, 64) : PF(64, 128);
@@ -893,16 +947,17 @@ int tllm_attention_biased_decode(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* positions,
     const int* token_slot, const int* rows, int n_rows, const int* block_table, int max_pages, int page_size,
     int q_heads, int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const float* sink_logit, int v_row, const void* gate, int gate_stride, int splits, float* part,
-    void* out, cudaStream_t stream) {
+    const float* slopes, const float* sink_logit, const float* dist_bias, int dist_len, int v_row, const void* gate,
+    int gate_stride, int splits, float* part, void* out, cudaStream_t stream) {
     if (v_row <= 0) v_row = dv;
+    TLLM_REQUIRE(dist_bias == nullptr || dist_len > 0, "attention_biased_decode: an empty table of biases");
     TLLM_REQUIRE(v_row >= dv && v_row % 8 == 0, "attention_biased_decode: values of width %d in rows of %d", dv, v_row);
     TLLM_REQUIRE(tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv), "attention_biased_decode: sizes %d/%d heads, widths %d/%d", q_heads, kv_heads, dk, dv);
     TLLM_REQUIRE(page_size > 0 && max_pages > 0 && n_rows >= 0 && kv_heads <= 65535, "attention_biased_decode: bad geometry");
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_decode: negative constant");
     TLLM_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || part != nullptr), "attention_biased_decode: %d runs of keys", splits);
     if (n_rows == 0) return 0;
-    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
+    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len};
 #define DEC(A, B) launch_biased_decode<A, B>(q, k_plane, v_plane, page_stride, positions, token_slot, rows, n_rows, block_table, \
                                              max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, \
                                              splits, part, out, stream)

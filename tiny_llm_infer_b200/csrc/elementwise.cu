@@ -204,6 +204,115 @@ __global__ void add_rmsnorm_vec_kernel(float* h, const TD* delta,
     }
 }
 
+// ---------------------------------------------------------------- scaled sum of several outputs + layer norm
+// For blocks whose sub-layers all read one norm's output and whose outputs are added together, each times a
+// vector of its own (a layer scale, a mixing weight, a residual multiplier, all folded into one float32 vector
+// per output):  v = h[r, :] + sum_i s_i[:] * d_i[r, :]  (float32, written back without `rows`),
+// out[o, :] = gain * (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps).  Rows as in add_rmsnorm.
+constexpr int kMaxScaledDeltas = 4;
+struct ScaledDeltas {
+    const void* d[kMaxScaledDeltas];
+    const float* s[kMaxScaledDeltas];
+    int n;
+};
+
+template <typename TD, typename TG, typename TO>
+__global__ void scaled_add_layernorm_kernel(float* h, ScaledDeltas ds, const TG* __restrict__ gain, float eps,
+                                            TO* __restrict__ out, const int* __restrict__ rows, int width) {
+    extern __shared__ float ln_row[];            // [width]
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    TO* dst = out + (size_t)o * width;
+    if (r < 0) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<TO>(0.0f);
+        return;
+    }
+    float* hr = h + (size_t)r * width;
+    const bool write_back = rows == nullptr && ds.n > 0;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = hr[i];
+        for (int k = 0; k < ds.n; ++k) v += ds.s[k][i] * to_f32<TD>(((const TD*)ds.d[k])[(size_t)r * width + i]);
+        if (write_back) hr[i] = v;
+        ln_row[i] = v;
+        sum += v;
+    }
+    const float mean = block_sum(sum, scratch) / (float)width;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = ln_row[i] - mean;
+        sq += d * d;
+    }
+    const float scale = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        dst[i] = from_f32<TO>(to_f32<TG>(gain[i]) * (ln_row[i] - mean) * scale);
+}
+
+// Vector form: the row stays in registers, CHUNKS groups of eight elements per thread.
+template <typename TD, typename TG, typename TO, int CHUNKS>
+__global__ void scaled_add_layernorm_vec_kernel(float* h, ScaledDeltas ds, const TG* __restrict__ gain, float eps,
+                                                TO* __restrict__ out, const int* __restrict__ rows, int width) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    TO* dst = out + (size_t)o * width;
+    const int n_chunks = width >> 3;
+    if (r < 0) {
+        const float zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) Vec8<TO>::store(dst + c * 8, zero);
+        return;
+    }
+    float* hr = h + (size_t)r * width;
+    const bool write_back = rows == nullptr && ds.n > 0;
+    float v[CHUNKS][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            Vec8<float>::load(hr + c * 8, v[j]);
+            for (int k = 0; k < ds.n; ++k) {
+                float d[8], s[8];
+                Vec8<TD>::load((const TD*)ds.d[k] + (size_t)r * width + c * 8, d);
+                Vec8<float>::load(ds.s[k] + c * 8, s);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[j][e] += s[e] * d[e];
+            }
+            if (write_back) Vec8<float>::store(hr + c * 8, v[j]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sum += v[j][e];
+        }
+    }
+    const float mean = block_sum(sum, scratch) / (float)width;
+    float sq = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[j][e] -= mean;
+                sq += v[j][e] * v[j][e];
+            }
+        }
+    }
+    const float scale = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            float g[8];
+            Vec8<TG>::load(gain + c * 8, g);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] = g[e] * v[j][e] * scale;
+            Vec8<TO>::store(dst + c * 8, g);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- norm of a sub-layer's output + add + RMSNorm
 // For blocks that norm a sub-layer's output before the residual sum ("sandwich" norms):
 // d' = post_gain * d / sqrt(mean(d^2) + post_eps);  v = h[r, :] + d';  out[o, :] = gain * v / sqrt(mean(v^2) + eps).
@@ -653,11 +762,66 @@ static int launch_postnorm_typed(float* h, const void* delta, const void* post_g
     return finish_launch("postnorm_add_rmsnorm");
 }
 
+template <typename TD, typename TG, typename TO>
+static int launch_scaled_layernorm_typed(float* h, const ScaledDeltas& ds, const void* gain, float eps, void* out,
+                                         const int* rows, int n_out, int width, cudaStream_t stream) {
+    bool vec = width % 8 == 0 && aligned16(h) && aligned16(gain) && aligned16(out);
+    for (int k = 0; k < ds.n; ++k) vec = vec && aligned16(ds.d[k]) && aligned16(ds.s[k]);
+    const int chunks = width / 8;
+    if (vec && chunks <= 1024 * 4) {
+        int block = 64;
+        while (block < 1024 && block < chunks) block *= 2;
+        const int per_thread = (chunks + block - 1) / block;
+#define VEC_LAUNCH(C)                                                                                         \
+    launch_pdl(kPdlNorm, scaled_add_layernorm_vec_kernel<TD, TG, TO, C>, dim3(n_out), dim3(block), 0, stream, \
+               h, ds, (const TG*)gain, eps, (TO*)out, rows, width)
+        if (per_thread <= 1) VEC_LAUNCH(1);
+        else if (per_thread <= 2) VEC_LAUNCH(2);
+        else VEC_LAUNCH(4);
+#undef VEC_LAUNCH
+    } else {
+        const size_t smem = (size_t)width * sizeof(float);
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(scaled_add_layernorm_kernel<TD, TG, TO>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) { set_error("scaled_add_layernorm: %s", cudaGetErrorString(e)); return (int)e; }
+        }
+        const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+        launch_pdl(kPdlNorm, scaled_add_layernorm_kernel<TD, TG, TO>, dim3(n_out), dim3(block), smem, stream,
+                   h, ds, (const TG*)gain, eps, (TO*)out, rows, width);
+    }
+    return finish_launch("scaled_add_layernorm");
+}
+
 }  // namespace tllm
 
 using namespace tllm;
 
 extern "C" {
+
+// h += sum over `n` outputs of scales[i] * deltas[i] (float32 vectors of the row's width; outputs in the
+// storage type), then the layer norm of the sum (mean taken off, gain, no bias).  `n` may be 0.
+int tllm_scaled_add_layernorm(float* h, const void* const* deltas, const float* const* scales, int n, const void* gain,
+                              int gain_dtype, float eps, void* out, int act_dtype, const int* rows, int n_out,
+                              int width, cudaStream_t stream) {
+    TLLM_REQUIRE(n_out >= 0 && width > 0 && n >= 0 && n <= kMaxScaledDeltas, "scaled_add_layernorm: bad sizes");
+    TLLM_REQUIRE(width <= 50 * 1024, "scaled_add_layernorm: rows of %d elements are too wide", width);
+    TLLM_REQUIRE(gain_dtype == kBF16 || gain_dtype == kF32, "scaled_add_layernorm: unknown gain dtype");
+    TLLM_REQUIRE(eps > 0.0f && gain != nullptr, "scaled_add_layernorm: eps must be positive and the gain given");
+    if (n_out == 0) return 0;
+    ScaledDeltas ds = {};
+    ds.n = n;
+    for (int k = 0; k < n; ++k) {
+        TLLM_REQUIRE(deltas[k] != nullptr && scales[k] != nullptr, "scaled_add_layernorm: missing operand");
+        ds.d[k] = deltas[k];
+        ds.s[k] = scales[k];
+    }
+#define LNORM(TD, TG, TO) launch_scaled_layernorm_typed<TD, TG, TO>(h, ds, gain, eps, out, rows, n_out, width, stream)
+    if (act_dtype == kBF16) return gain_dtype == kBF16 ? LNORM(bf16, bf16, bf16) : LNORM(bf16, float, bf16);
+    if (act_dtype == kF32) return gain_dtype == kBF16 ? LNORM(float, bf16, float) : LNORM(float, float, float);
+#undef LNORM
+    TLLM_REQUIRE(false, "scaled_add_layernorm: unknown dtype %d", act_dtype);
+}
 
 const char* tllm_last_error() { return g_error; }
 

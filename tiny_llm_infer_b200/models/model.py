@@ -65,7 +65,7 @@ class Model:
             for role, spec in layer.parts.items():
                 parts[role] = _make(roles[role], spec, dtype, device)
                 self._parts.append((spec, parts[role]))
-            self.blocks.append(registry.lookup("block", layer.block)(parts))
+            self.blocks.append(registry.lookup("block", layer.block)(parts, **layer.params))
         self.final_norm = _make("norm", desc.final_norm, dtype, device)
         self.head = _make("head", desc.head, dtype, device)
         self._parts += [(desc.final_norm, self.final_norm), (desc.head, self.head)]

@@ -64,21 +64,25 @@ def _declare(h) -> None:
         "tllm_embedding": [vp, vp, i32, vp, i32, i32, i32, f32, vp],
         "tllm_postnorm_add_rmsnorm": [vp, vp, vp, f32, vp, i32, f32, vp, i32, vp, i32, i32, vp],
         "tllm_qkv_unit_store": [vp, i32, vp, vp, f32, i32, vp, vp, vp, i32, i32, vp, vp, i64, vp, i32, i32,
-                                i32, i32, i32, i32, i32, vp],
+                                i32, i32, i32, i32, i32, vp, i32, f32, i32, i32, vp],
         "tllm_attention_biased_general": [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32,
-                                          f32, f32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp],
+                                          f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, vp, vp],
         "tllm_attention_biased_prefill": [vp, vp, vp, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                                          f32, f32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp],
+                                          f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, vp, vp],
         "tllm_attention_biased_decode": [vp, vp, vp, i64, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                                         f32, f32, i32, i32, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp],
+                                         f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, i32, vp, vp, vp],
+        "tllm_scaled_add_layernorm": [vp, vp, vp, i32, vp, i32, f32, vp, i32, vp, i32, i32, vp],
+        "tllm_linear_prepare": [vp, i32, i32, vp, i32, vp, i32, f32, vp, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp,
+                                i32, vp],
         "tllm_embedding_norm": [vp, vp, vp, vp, i32, vp, f32, f32, vp, i32, i32, i32, i32, vp],
         "tllm_softcap": [vp, f32, i64, vp],
         "tllm_stream_add": [vp, vp, vp, i32, f32, vp, i32, i32, i32, vp],
         "tllm_activation": [vp, vp, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp],
         "tllm_delta_prepare": [vp, i32, i32, vp, vp, i32, vp, i32, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, f32,
-                               vp, vp, vp, vp, vp, i32, vp],
-        "tllm_delta_scan": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp, vp],
-        "tllm_delta_finish": [vp, vp, i32, vp, f32, vp, i32, i32, i32, i32, i32, vp, i32, vp, i32, i32, vp, i64, vp],
+                               vp, vp, vp, vp, vp, i32, i32, i32, vp],
+        "tllm_delta_scan": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp, i32, vp, i64, f32, vp, vp],
+        "tllm_delta_finish": [vp, vp, i32, i32, vp, f32, vp, i32, i32, i32, i32, i32, vp, i32, vp, i32, i32, vp, i64,
+                              vp, i32, i32, vp],
         "tllm_latent_norm_store": [vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, vp, f32, vp, vp, vp, i32, i32,
                                    vp, i64, vp, i32, i32, vp],
         "tllm_latent_query": [vp, vp, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, vp],
@@ -201,6 +205,26 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tens
         return out
     _check(lib().tllm_add_rmsnorm(_p(h), _p(delta), _p(gain), _dt(gain), float(eps), _p(out), _dt(out),
                                   _p(rows), n_out, h.shape[-1], _stream()), "add_rmsnorm")
+    return out
+
+
+def scaled_add_layernorm(h: torch.Tensor, deltas, scales, gain: torch.Tensor, eps: float, out: torch.Tensor,
+                         rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h += sum_i scales[i] * deltas[i] (float32, written back; ``scales[i]`` a float32 vector of the row's width,
+    ``deltas[i]`` [T, width] in the storage type; at most four), then out = gain * (h - mean) / sqrt(mean of the
+    squared deviations + eps).  With ``rows`` only those rows are normed, into out[0..len(rows)), and h is not
+    written."""
+    _cuda(h, gain, out, rows, *deltas, *scales)
+    assert h.dtype == torch.float32 and len(deltas) == len(scales) <= 4
+    for d, s in zip(deltas, scales):
+        assert d.dtype == out.dtype and d.shape == h.shape and s.dtype == torch.float32 and s.numel() == h.shape[1]
+    n = len(deltas)
+    dp = (ctypes.c_void_p * 4)(*[d.data_ptr() for d in deltas])
+    sp = (ctypes.c_void_p * 4)(*[s.data_ptr() for s in scales])
+    n_out = out.shape[0] if rows is None else rows.numel()
+    _check(lib().tllm_scaled_add_layernorm(_p(h), ctypes.cast(dp, ctypes.c_void_p), ctypes.cast(sp, ctypes.c_void_p), n,
+                                           _p(gain), _dt(gain), float(eps), _p(out), _dt(out), _p(rows), n_out,
+                                           h.shape[-1], _stream()), "scaled_add_layernorm")
     return out
 
 
@@ -629,12 +653,21 @@ def qkv_unit_store(proj: torch.Tensor, q_out: torch.Tensor, positions, token_slo
                    k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], page_size: int,
                    q_heads: int, kv_heads: int, dk: int, dv: int, eps: Optional[float],
                    q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
-                   store: bool = True) -> None:
+                   store: bool = True, inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0,
+                   q_temperature=None, values_are_keys: bool = False) -> None:
     """Rows of ``proj`` = q heads | k heads | v heads | anything: queries and keys divided per head by
     their root mean square (``eps`` None: left as they are; gains optional), queries to ``q_out``,
     keys and values of every row into their planes of the paged cache (``store``).  Keys have width
-    ``dk``, values ``dv``.  Rows with a negative slot are skipped."""
-    _cuda(proj, q_out, positions, token_slot, block_table, q_gain, k_gain)
+    ``dk``, values ``dv``.  Rows with a negative slot are skipped.  ``inv_freq`` [rot_dims / 2] float32: the first
+    ``rot_dims`` elements of every query and key head turn by position * inv_freq (pairs half the rotated width
+    apart), after the norm.  ``q_temperature`` (coef, every): queries times 1 + coef ln(floor((pos + 1) / every) + 1).
+    ``values_are_keys``: the rows carry no values; a value is its key as projected, before the norm (dv = dk)."""
+    _cuda(proj, q_out, positions, token_slot, block_table, q_gain, k_gain, inv_freq)
+    if inv_freq is not None:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2
+    if q_gain is not None:
+        assert q_gain.dtype == k_gain.dtype == proj.dtype
+    coef, every = q_temperature if q_temperature is not None else (0.0, 0)
     assert q_out.dtype == proj.dtype and tuple(q_out.shape) == (proj.shape[0], q_heads * dk)
     kp = vp = None
     stride = 0
@@ -646,8 +679,9 @@ def qkv_unit_store(proj: torch.Tensor, q_out: torch.Tensor, positions, token_slo
     _check(lib().tllm_qkv_unit_store(
         _p(proj), proj.shape[1], _p(q_gain), _p(k_gain), float(eps or 1.0), int(eps is not None), _p(positions),
         _p(token_slot), _p(block_table), block_table.shape[1] if block_table is not None else 0, page_size,
-        kp, vp, stride, _p(q_out), _dt(proj), proj.shape[0], q_heads, kv_heads, dk, dv, int(store), _stream()),
-        "qkv_unit_store")
+        kp, vp, stride, _p(q_out), _dt(proj), proj.shape[0], q_heads, kv_heads, dk, dv, int(store),
+        _p(inv_freq), int(rot_dims if inv_freq is not None else 0), float(coef), int(every), int(values_are_keys),
+        _stream()), "qkv_unit_store")
 
 
 def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, positions, token_slot,
@@ -655,7 +689,7 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
                      out: torch.Tensor, softcap: float = 0.0, chunk: int = 0, window: int = 0,
                      sink: bool = False, slopes: Optional[torch.Tensor] = None,
                      gate: Optional[torch.Tensor] = None, ctx=None, sink_logits: Optional[torch.Tensor] = None,
-                     values_in_keys: bool = False) -> torch.Tensor:
+                     values_in_keys: bool = False, distance_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of every row of ``q`` [T, q_heads * dk] over the keys of its own request, with the
     score s = (q . k) * scale changed in this order by whatever is given: ``softcap`` (s <- cap *
     tanh(s / cap)), ``slopes`` [q_heads] float32 (s <- s - slope * (pos - key pos)); keys j <= pos from
@@ -663,8 +697,14 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
     denominator, or exp(sink_logits[head]) with ``sink_logits`` [q_heads] float32 (a learned score that is
     neither scaled nor capped).  ``gate`` (a view [T, q_heads * dv] whose rows may be strided): out *=
     sigmoid(gate).  ``values_in_keys``: a value is the first ``dv`` elements of its key's row (``v_plane`` is
-    not looked at), as in attention over compressed vectors that are key and, in part, value at once."""
-    _cuda(q, positions, token_slot, block_table, out, slopes, sink_logits)
+    not looked at), as in attention over compressed vectors that are key and, in part, value at once.
+    ``distance_bias`` [q_heads, L] float32: entry [h, min(pos - key pos, L - 1)] is added to the score after
+    everything else (a learned bias by distance; it is not scaled)."""
+    _cuda(q, positions, token_slot, block_table, out, slopes, sink_logits, distance_bias)
+    dist_len = 0
+    if distance_bias is not None:
+        assert distance_bias.dtype == torch.float32 and distance_bias.dim() == 2 and distance_bias.shape[0] == q_heads
+        dist_len = distance_bias.shape[1]
     tokens = q.shape[0]
     assert tuple(out.shape) == (tokens, q_heads * dv) and out.dtype == q.dtype
     kp, stride = _plane(k_plane)
@@ -684,7 +724,7 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
         assert slopes.dtype == torch.float32 and slopes.numel() == q_heads
     gate_ptr = None if gate is None else gate.data_ptr()
     mods = (float(scale), float(softcap or 0.0), int(chunk or 0), int(window or 0), int(bool(sink)), _p(slopes),
-            _p(sink_logits), v_row, gate_ptr, gate_stride)
+            _p(sink_logits), _p(distance_bias), dist_len, v_row, gate_ptr, gate_stride)
     consts = mods + (_p(out), _stream())
     if BIASED_FAST and ctx is not None and ctx.pf_tiles is not None and ctx.tokens == tokens \
             and q.dtype == torch.bfloat16 and gate_stride % 2 == 0 and v_row % 8 == 0 \
@@ -708,7 +748,7 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
     _check(lib().tllm_attention_biased_general(
         _p(q), kp, vp, stride, _p(positions), _p(token_slot), _p(block_table), block_table.shape[1], page_size,
         _dt(q), tokens, q_heads, kv_heads, dk, dv, float(scale), float(softcap or 0.0), int(chunk or 0),
-        int(window or 0), int(bool(sink)), _p(slopes), _p(sink_logits), v_row,
+        int(window or 0), int(bool(sink)), _p(slopes), _p(sink_logits), _p(distance_bias), dist_len, v_row,
         None if gate is None else gate.data_ptr(), gate_stride, _p(out), _stream()), "attention_biased")
     return out
 
@@ -797,22 +837,41 @@ def delta_rule_state_floats(heads: int, kv_heads: int, dk: int, dv: int, taps: i
     return int(lib().tllm_delta_rule_state_floats(heads, kv_heads, dk, dv, taps))
 
 
+SCAN_DELTA, SCAN_PLAIN, SCAN_MEMORY = 0, 1, 2        # recurrences of the scan kernel (csrc/delta_rule.cu, ScanMode)
+GATE_ACTS = {"sigmoid": 0, "silu": 1}                # what the read-out is multiplied by: act(gate)
+
+
+def _delta_finish(o_raw, gate, out_weight, weight_per_head, eps, token_slot, tokens, heads, kv_heads, dk, dv, out_dtype,
+                  proj, ld, taps, state, den, gate_act):
+    out = torch.empty((tokens, heads * dv), dtype=out_dtype, device=o_raw.device)
+    assert gate.stride(1) == 1 and gate.dtype in (torch.float32, out_dtype) and out_weight.dtype == torch.float32
+    assert out_weight.numel() == (heads * dv if weight_per_head else dv)
+    _check(lib().tllm_delta_finish(_p(o_raw), gate.data_ptr(), int(gate.dtype == torch.float32), gate.stride(0), _p(out_weight),
+                                   float(eps), _p(token_slot), tokens, heads, kv_heads, dk, dv, _p(out), _dt(out), _p(proj), ld,
+                                   taps, _p(state), state.stride(0), _p(den), GATE_ACTS[gate_act],
+                                   dv if weight_per_head else 0, _stream()), "delta_finish")
+    return out
+
+
 def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, a: torch.Tensor, dt_bias: torch.Tensor,
                rate: torch.Tensor, gate: torch.Tensor, out_weight: torch.Tensor, eps: float, token_slot: torch.Tensor,
                seg_info: Optional[torch.Tensor], state: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int,
-               q_scale: float, unit_eps: float, out_dtype: torch.dtype, conv_t: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One step of the delta rule with a decay per head and key channel for every row of ``proj`` [T, >= channels
-    + heads] = q channels | k channels | v channels | beta logits (storage type): convolution with ``conv_w``
-    [channels, taps] and SiLU, unit q and k, g = exp(-rate_h softplus(a + dt_bias)) with ``a`` [T, heads * dk]
-    float32, the recurrence over each portion's rows from ``state[slot]`` (float32, updated in place), then the
-    read-out divided by its root mean square per head, times ``out_weight`` [dv] float32, times sigmoid(``gate``)
-    ([T, heads * dv] float32, rows may be strided).  ``seg_info`` [segments, 4] = slot, first row, length, first
-    position; None: every row is a portion of one token.  ``conv_t``: the taps once more as [taps, channels],
-    which lets the kernels take eight channels per access.  Returns [T, heads * dv] in ``out_dtype``."""
+               q_scale: float, unit_eps: float, out_dtype: torch.dtype, conv_t: Optional[torch.Tensor] = None,
+               decay_per_head: bool = False, beta_col: Optional[int] = None, gate_act: str = "sigmoid") -> torch.Tensor:
+    """One step of the delta rule for every row of ``proj`` [T, >= channels + heads] = q channels | k channels | v
+    channels | ... with the beta logits at column ``beta_col`` (None: right behind the channels), in the storage
+    type: convolution with ``conv_w`` [channels, taps] and SiLU, unit q and k, g = exp(-rate_h softplus(a + dt_bias))
+    with ``a`` float32 [T, heads * dk] (a decay per head and key channel) or, ``decay_per_head``, [T, heads]; the
+    recurrence over each portion's rows from ``state[slot]`` (float32, updated in place), then the read-out divided
+    by its root mean square per head, times ``out_weight`` [dv] float32, times ``gate_act``(``gate``) ([T, heads * dv]
+    float32 or storage type, rows may be strided).  ``seg_info`` [segments, 4] = slot, first row, length, first
+    position; None: every row is a portion of one token.  ``conv_t``: the taps once more as [taps, channels], which
+    lets the kernels take eight channels per access.  Returns [T, heads * dv] in ``out_dtype``."""
     _cuda(proj, conv_w, dt_bias, rate, out_weight, token_slot, seg_info, state, conv_t)
     tokens, ld = proj.shape
-    assert a.dtype == gate.dtype == dt_bias.dtype == rate.dtype == out_weight.dtype == state.dtype == torch.float32
-    assert a.stride(1) == 1 and gate.stride(1) == 1 and conv_w.dtype == proj.dtype and state.dim() == 2
+    assert a.dtype == dt_bias.dtype == rate.dtype == out_weight.dtype == state.dtype == torch.float32
+    assert a.stride(1) == 1 and conv_w.dtype == proj.dtype and state.dim() == 2
+    assert dt_bias.numel() == (heads if decay_per_head else heads * dk)
     dev = proj.device
     ws = workspace(dev, tokens * (2 * kv_heads * dk + 2 * heads * dv + heads * dk + heads))
     at = 0
@@ -827,16 +886,75 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, a: torch.Ten
                                       take(heads * dv), take(heads))
     _check(lib().tllm_delta_prepare(_p(proj), ld, _dt(proj), _p(conv_w), _p(conv_t), taps, a.data_ptr(), a.stride(0), _p(dt_bias), _p(rate),
                                     _p(token_slot), _p(state), state.stride(0), heads, kv_heads, dk, dv, float(q_scale),
-                                    float(unit_eps), _p(qn), _p(kn), _p(vv), _p(decay), _p(beta), tokens, _stream()),
+                                    float(unit_eps), _p(qn), _p(kn), _p(vv), _p(decay), _p(beta), tokens,
+                                    int(decay_per_head), -1 if beta_col is None else int(beta_col), _stream()),
            "delta_prepare")
     segments = tokens if seg_info is None else seg_info.shape[0]
     _check(lib().tllm_delta_scan(_p(seg_info), segments, _p(token_slot), _p(qn), _p(kn), _p(vv), _p(decay), _p(beta),
-                                 _p(state), state.stride(0), heads, kv_heads, dk, dv, _p(o_raw), _stream()), "delta_scan")
-    out = torch.empty((tokens, heads * dv), dtype=out_dtype, device=dev)
-    _check(lib().tllm_delta_finish(_p(o_raw), gate.data_ptr(), gate.stride(0), _p(out_weight), float(eps), _p(token_slot),
-                                   tokens, heads, kv_heads, dk, dv, _p(out), _dt(out), _p(proj), ld, taps, _p(state),
-                                   state.stride(0), _stream()), "delta_finish")
-    return out
+                                 _p(state), state.stride(0), heads, kv_heads, dk, dv, _p(o_raw), SCAN_DELTA, None, 0, 0.0,
+                                 None, _stream()), "delta_scan")
+    return _delta_finish(o_raw, gate, out_weight, False, eps, token_slot, tokens, heads, kv_heads, dk, dv, out_dtype,
+                         proj, ld, taps, state, None, gate_act)
+
+
+LINEAR_KINDS = {"channel_decay": 0, "log_gates": 1}      # csrc/delta_rule.cu, LinearKind
+
+
+def linear_recurrence_state_floats(kind: str, heads: int, dk: int, dv: int) -> int:
+    """Float32 words of one request's state of ``linear_recurrence``: S of every head in the scan kernel's layout
+    (with ``log_gates`` one more column, the normaliser) and, with ``log_gates``, the running maximum per column."""
+    cols = dv + 1 if kind == "log_gates" else dv
+    s_floats = delta_rule_state_floats(heads, heads, dk, cols, 1)
+    return s_floats + (heads * cols if kind == "log_gates" else 0)
+
+
+def linear_recurrence(proj: torch.Tensor, kind: str, z: torch.Tensor, z_bias: torch.Tensor, p0: float,
+                      gate: torch.Tensor, gate_act: str, out_weight: torch.Tensor, weight_per_head: bool, eps: float,
+                      token_slot: torch.Tensor, seg_info: Optional[torch.Tensor], state: torch.Tensor, heads: int,
+                      dk: int, dv: int, q_scale: float, out_dtype: torch.dtype, floor_eps: float = 1e-6) -> torch.Tensor:
+    """One step of a recurrence S <- decay S + k (w v)^T, o = S^T q per head, for every row of ``proj`` [T, >= heads
+    (2 dk + dv)] = q | k | v in the storage type (q is multiplied by ``q_scale``), from ``state[slot]`` (float32,
+    updated in place).  ``kind``:
+
+    * ``channel_decay``: a decay per key channel sigmoid(z + z_bias)^p0 with ``z`` [T, heads * dk] float32, w = 1;
+    * ``log_gates``: ``z`` [T, 2 heads] float32 = write | keep logits (plus ``z_bias``), each capped as p0 tanh(. /
+      p0); with i the capped write logit and f = logsigmoid(capped keep logit), a running maximum m <- max(f + m, i)
+      that starts at zero: decay = exp(f + m_before - m), w = exp(i - m); a vector n <- decay n + w k is kept beside
+      S and the read-out is S^T q / (max(|n . q|, exp(-m)) + ``floor_eps``).
+
+    Then the read-out is divided by its root mean square per head (``eps``), times ``out_weight`` ([dv], or [heads *
+    dv] with ``weight_per_head``) float32, times ``gate_act``(``gate``) ([T, heads * dv], rows may be strided).
+    Returns [T, heads * dv] in ``out_dtype``."""
+    _cuda(proj, z_bias, out_weight, token_slot, seg_info, state)
+    tokens, ld = proj.shape
+    assert z.dtype == z_bias.dtype == state.dtype == torch.float32 and z.stride(1) == 1 and state.dim() == 2
+    memory = kind == "log_gates"
+    cols = dv + 1 if memory else dv
+    assert state.shape[1] == linear_recurrence_state_floats(kind, heads, dk, dv)
+    dev = proj.device
+    ws = workspace(dev, tokens * (3 * heads * dk + heads * (cols + dv) + 3 * heads + 8))
+    at = 0
+
+    def take(n):
+        nonlocal at
+        t = ws[at:at + tokens * n]
+        at += -(-tokens * n // 4) * 4
+        return t
+    qn, kn = take(heads * dk), take(heads * dk)
+    decay = None if memory else take(heads * dk)
+    vv, o_raw = take(heads * cols), take(heads * dv)
+    wgate, fgate, den = (take(heads), take(heads), take(heads)) if memory else (None, None, None)
+    _check(lib().tllm_linear_prepare(_p(proj), ld, _dt(proj), z.data_ptr(), z.stride(0), _p(z_bias), LINEAR_KINDS[kind],
+                                     float(p0), _p(token_slot), heads, dk, dv, float(q_scale), _p(qn), _p(kn), _p(vv),
+                                     _p(decay), _p(wgate), _p(fgate), tokens, _stream()), "linear_prepare")
+    segments = tokens if seg_info is None else seg_info.shape[0]
+    aux_off = delta_rule_state_floats(heads, heads, dk, cols, 1) if memory else 0
+    _check(lib().tllm_delta_scan(_p(seg_info), segments, _p(token_slot), _p(qn), _p(kn), _p(vv), _p(decay), _p(wgate),
+                                 _p(state), state.stride(0), heads, heads, dk, cols, _p(o_raw),
+                                 SCAN_MEMORY if memory else SCAN_PLAIN, _p(fgate), aux_off, float(floor_eps), _p(den),
+                                 _stream()), "delta_scan")
+    return _delta_finish(o_raw, gate, out_weight, weight_per_head, eps, token_slot, tokens, heads, heads, dk, dv,
+                         out_dtype, None, 0, 1, state, den, gate_act)
 
 
 # --------------------------------------------------------------------------- attention over compressed vectors

@@ -2,6 +2,7 @@
 arrangements, each with its sizes and constants as parameters and none aware of the
 model it is used in.  Importing this package registers the built-in parts."""
 from . import (attention, attention_biased, block, delta_rule, embedding, feed_forward, latent_attention,  # noqa: F401
+               linear_recurrence,
                moe, norm, position)
 from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, lookup, register,
                        unregister)

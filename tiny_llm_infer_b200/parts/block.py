@@ -17,6 +17,13 @@ side input (a feed-forward that also looks at the step's tokens) are each there 
 ``stream_mixer_ffn``, ``stream_mixer_side``, ``stream_mixer_ffn_side``.  Every sum is one kernel that norms the
 output, adds it in float32 and hands the stream on in the storage type; the last output goes on as a
 ``NormedDelta`` like the sandwich's.
+
+``parallel_*``: one norm, and every sub-layer reads its output: with x = norm1(h),
+h += m * (ls1 * sum_i c_i mixer_i(x) + ls2 * ffn(x)), where ls1 and ls2 are learned vectors (``column_scale``
+parts), the c_i weigh the mixers and m is the residual multiplier.  One mixer (``parallel_mixer``,
+``parallel_mixer_ffn``) or two side by side (``parallel_pair``, ``parallel_pair_ffn``, roles ``left`` and
+``right``, each with a cache of its own).  The outputs go on as ``ScaledDeltas``: the norm kernel that follows
+multiplies, adds in float32 and norms in one pass.
 """
 from __future__ import annotations
 
@@ -25,7 +32,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from .norm import NormedDelta
+from .norm import NormedDelta, ScaledDeltas
 from .registry import register
 
 
@@ -114,3 +121,46 @@ def _stream_block(name: str, with_ffn: bool, with_side: bool) -> type:
 for _ffn in (False, True):
     for _side in (False, True):
         _stream_block("stream_mixer" + ("_ffn" if _ffn else "") + ("_side" if _side else ""), _ffn, _side)
+
+
+def _parallel_block(name: str, mixer_roles, with_ffn: bool) -> type:
+    roles = {"norm1": "norm"}
+    roles.update({role: "mixer" for role in mixer_roles})
+    roles["ls1"] = "norm"
+    if with_ffn:
+        roles.update({"ffn": "feed_forward", "ls2": "norm"})
+
+    class ParallelBlock(Block):
+        def __init__(self, parts: Dict[str, object], residual_mult: float = 1.0, mixer_weights=None):
+            super().__init__(parts)
+            self.residual_mult = float(residual_mult)
+            self.mixer_weights = [1.0] * len(mixer_roles) if mixer_weights is None else [float(w) for w in mixer_weights]
+            if len(self.mixer_weights) != len(mixer_roles):
+                raise ValueError(f"{len(self.mixer_weights)} weights for {len(mixer_roles)} mixers")
+            self._scales: Optional[List[torch.Tensor]] = None
+
+        def scales(self) -> List[torch.Tensor]:
+            """Per output the float32 vector it is multiplied by before the sum (made once, after the load)."""
+            if self._scales is None:
+                out = [self.ls1.scale * (self.residual_mult * w) for w in self.mixer_weights]
+                if with_ffn:
+                    out.append(self.ls2.scale * self.residual_mult)
+                self._scales = [v.contiguous() for v in out]
+            return self._scales
+
+        def forward(self, h: torch.Tensor, pending, ctx, cache):
+            x = self.norm1.forward(h, pending)
+            views = cache if isinstance(cache, (list, tuple)) else [cache]
+            deltas = [mixer.forward(x, ctx, view) for mixer, view in zip(self.mixers(), views)]
+            if with_ffn:
+                deltas.append(self.ffn.forward(x, ctx))
+            return ScaledDeltas(deltas, self.scales())
+
+    ParallelBlock.roles = roles
+    ParallelBlock.__name__ = ParallelBlock.__qualname__ = "".join(w.title() for w in name.split("_")) + "Block"
+    return register("block", name)(ParallelBlock)
+
+
+for _roles, _name in ((("mixer",), "parallel_mixer"), (("left", "right"), "parallel_pair")):
+    for _ffn in (False, True):
+        _parallel_block(_name + ("_ffn" if _ffn else ""), _roles, _ffn)

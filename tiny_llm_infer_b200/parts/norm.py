@@ -18,7 +18,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
 import torch
 
@@ -66,3 +66,62 @@ class RMSNorm:
             post = delta.gain if delta.gain.dtype == self.gain.dtype else delta.gain.to(self.gain.dtype)
             return ops.add_rmsnorm(h, delta.delta, self.gain, self.eps, out, rows, post_gain=post, post_eps=delta.eps)
         return ops.add_rmsnorm(h, delta, self.gain, self.eps, out, rows)
+
+
+@dataclass
+class ScaledDeltas:
+    """Outputs of sub-layers that all read one norm's output, each still to be multiplied column by column by a
+    float32 vector of its own (layer scale, mixing weight and residual multiplier folded into one) and added to
+    the stream, by the norm that follows."""
+    deltas: List[torch.Tensor]
+    scales: List[torch.Tensor]
+
+
+@register("norm", "layernorm")
+class LayerNorm:
+    """x = gain * (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps), no bias, fused with the residual sum that
+    precedes it: ``delta`` is None, one output in the storage type (added as it is), or ``ScaledDeltas``.  The
+    sum, the mean and the variance are float32."""
+
+    def __init__(self, width: int, eps: float, dtype: torch.dtype, device, name: str = "weight"):
+        self.width, self.eps, self.dtype, self.device, self.name = int(width), float(eps), dtype, device, name
+        self.gain: Optional[torch.Tensor] = None
+        self._ones: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_specs(cls, width: int, eps: float, name: str = "weight") -> Dict[str, ParamSpec]:
+        return {name: ParamSpec((int(width),), "norm")}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.gain = tensors[self.name].contiguous()
+
+    def forward(self, h: torch.Tensor, delta, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.width), dtype=self.dtype, device=h.device)
+        if delta is None:
+            deltas, scales = [], []
+        elif isinstance(delta, ScaledDeltas):
+            deltas, scales = delta.deltas, delta.scales
+        else:
+            if self._ones is None:
+                self._ones = torch.ones(self.width, dtype=torch.float32, device=h.device)
+            deltas, scales = [delta], [self._ones]
+        return ops.scaled_add_layernorm(h, deltas, scales, self.gain, self.eps, out, rows)
+
+
+@register("norm", "column_scale")
+class ColumnScale:
+    """A learned vector that a sub-layer's output is multiplied by, column by column, before the residual sum
+    (a layer scale).  It has no ``forward``: the block folds it, with its other constants, into the vector that
+    the next norm's kernel applies (``ScaledDeltas``)."""
+
+    def __init__(self, width: int, dtype: torch.dtype, device, name: str = "weight"):
+        self.width, self.dtype, self.device, self.name = int(width), dtype, device, name
+        self.scale: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_specs(cls, width: int, name: str = "weight") -> Dict[str, ParamSpec]:
+        return {name: ParamSpec((int(width),), "norm")}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.scale = tensors[self.name].to(torch.float32).contiguous()

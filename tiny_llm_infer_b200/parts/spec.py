@@ -34,9 +34,11 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement and the parts it arranges."""
+    """One layer: a block arrangement, the parts it arranges and the arrangement's own constants
+    (``params``: keyword arguments of the block class beside its parts; most blocks have none)."""
     block: str
     parts: Dict[str, PartSpec]
+    params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
