@@ -28,6 +28,7 @@ For more than one GPU this engine has nothing to run: it prints one line and exi
 """
 import argparse
 import json
+import math
 import statistics
 import subprocess
 import sys
@@ -888,6 +889,255 @@ def kaketar_bench(args) -> int:
     return 0
 
 
+TETODRA_SIZES = {
+    # width, layers in the order parallel, parallel_2, delta, parallel_2 (repeated), feed-forward on every layer;
+    # both attentions: heads, key/value heads, head width (keys and values); both side memories: heads, key and value
+    # width; delta rule: heads, heads of queries and keys, widths, taps
+    "1b": dict(width=2048, layers=8, ff=6144, vocab=32768, a_heads=16, a_kv=4, a_dim=128, m_heads=8, m_dim=128, m_vdim=128,
+               d_heads=16, d_kv=8, d_dim=128, d_vdim=128, taps=4),
+    "8b": dict(width=4096, layers=4, ff=12288, vocab=32768, a_heads=32, a_kv=8, a_dim=128, m_heads=16, m_dim=128, m_vdim=128,
+               d_heads=32, d_kv=16, d_dim=128, d_vdim=128, taps=4),
+}
+
+
+def _model_costs(cfg, context):
+    """(weights a token multiplies with, cache bytes a decode row reads per token of its context, bytes of a
+    request's fixed-size state), from the model's own description: every matrix once (the tied head counts as the
+    embedding; other look-up tables do not), the planes of every cache within its reach, every state."""
+    import torch
+    from tiny_llm_infer_b200.config import describe_model
+    from tiny_llm_infer_b200.models.model import Model, expected_tensors
+    desc = describe_model(cfg)
+    names, _ = expected_tensors(desc)
+    params = sum(math.prod(spec.shape) for name, spec in names.items()
+                 if len(spec.shape) == 2 and not (name.endswith("embed") and name != desc.embedding.prefix + desc.embedding.params.get("name", "")))
+    kv = state = 0.0
+    for cache, st in Model(desc, torch.bfloat16, None).cache_needs().values():
+        if cache is not None:
+            reach = min(cache.window or context, context)
+            kv += 2.0 * sum(h * w for h, w in cache.planes) * reach / context
+        if st is not None:
+            state += 4.0 * math.prod(st.shape)
+    return params, kv, state
+
+
+def _kaketar_at(z):
+    from tiny_llm_infer_b200.config.kaketar import (ChannelDeltaConfig, DenseConfig, KaketarConfig, KaketarLayerConfig,
+                                                     LatentAttentionConfig, RotationScaling)
+    dmix = ChannelDeltaConfig(z["d_heads"], z["d_heads"], z["d_dim"], z["d_vdim"], z["taps"], z["rank"], z["rank"])
+    amix = LatentAttentionConfig(z["a_heads"], z["a_dim"], z["a_rot"], z["a_vdim"], z["q_rank"], z["kv_rank"],
+                                 1.0 / math.sqrt(z["a_dim"] + z["a_rot"]), 10000.0, z["a_rot"], z["window"],
+                                 RotationScaling(4.0, 1024.0, 32.0, 1.0))
+    return KaketarConfig(vocab=z["vocab"], width=z["width"], max_positions=4096, embedding_scale=1.0, norm_eps=1e-6, layers=tuple(
+        KaketarLayerConfig("latent_attention", amix, DenseConfig(z["ff"])) if i % 4 == 3 else
+        KaketarLayerConfig("channel_delta", dmix, DenseConfig(z["ff"])) for i in range(z["layers"])),
+        logit_softcap=30.0, side_dim=z["side"])
+
+
+def tetodra_bench(args) -> int:
+    """``--design tetodra``: prefill and decode throughput of the Tetodra design at sizes that resemble a real
+    model's layers (random weights, bfloat16; layers in the order attention with keys as values beside a matrix
+    memory, attention with a rotation beside gated linear attention, delta rule with a decay per head, the second
+    kind again; a feed-forward on every layer), beside the two closest models the engine has at equal width,
+    layers, feed-forward and vocabulary, through the same step function: Kaketar (delta rule and attention, its
+    own bench's sizes) and Qwen3 dense.  Then the design's kernels one by one beside their relatives, with their
+    share of the measured peaks.  One JSON line."""
+    import torch
+    from tiny_llm_infer_b200 import ops
+    from tiny_llm_infer_b200.config import Qwen3Config
+    from tiny_llm_infer_b200.config.tetodra import (DenseConfig, GatedDeltaConfig, GatedLinearConfig, KeyValueAttentionConfig,
+                                                     MatrixMemoryConfig, PairConfig, RotaryAttentionConfig, TetodraConfig,
+                                                     TetodraLayerConfig)
+    from tiny_llm_infer_b200.engine.batch import StepContext
+    from tiny_llm_infer_b200.parts.attention_biased import distance_buckets
+    from tiny_llm_infer_b200.parts.delta_rule import state_floats
+
+    hx = _DesignHarness(args)
+    device, pk, clocks, windows = hx.device, hx.pk, hx.clocks, hx.windows
+    tokens_pf, batch, context, steps, warmup = hx.tokens_pf, hx.batch, hx.context, hx.steps, hx.warmup
+    timed, run_model = hx.timed, hx.run_model
+    record = {"sizes": {}}
+    for size_name in ([args.model] if args.model in TETODRA_SIZES else sorted(TETODRA_SIZES)):
+        z = TETODRA_SIZES[size_name]
+        L, W, D = z["layers"], z["width"], z["a_dim"]
+        ff = DenseConfig(z["ff"])
+        keyed = PairConfig(KeyValueAttentionConfig(z["a_heads"], z["a_kv"], D, D, D ** -0.5, 128.0, 0.25, 512, 32),
+                           MatrixMemoryConfig(z["m_heads"], z["m_dim"], z["m_vdim"], 12.0), 0.5, 1.0)
+        rotary = PairConfig(RotaryAttentionConfig(z["a_heads"], z["a_kv"], D, D, D ** -0.5, 1000000.0, D),
+                            GatedLinearConfig(z["m_heads"], z["m_dim"], z["m_vdim"], 8.0, W // 64), 0.75, 0.75)
+        delta = GatedDeltaConfig(z["d_heads"], z["d_kv"], z["d_dim"], z["d_vdim"], z["taps"])
+        kinds = [("parallel", keyed), ("parallel_2", rotary), ("delta", delta), ("parallel_2", rotary)]
+        tcfg = TetodraConfig(vocab=z["vocab"], width=W, embedding_scale=1.0, norm_eps=1e-5, residual_mult=0.8,
+                             layers=tuple(TetodraLayerConfig(*kinds[i % 4], ff) for i in range(L)))
+        H, G = z["a_heads"], z["a_kv"]
+        qcfg = Qwen3Config(hidden_size=W, intermediate_size=z["ff"], num_hidden_layers=L, num_attention_heads=H,
+                           num_key_value_heads=G, head_dim=D, vocab_size=z["vocab"], max_position_embeddings=8192,
+                           tie_word_embeddings=True, layer_types=("full_attention",) * L)
+        kcfg = _kaketar_at(KAKETAR_SIZES[size_name])
+        q_params = L * (W * (H + 2 * G) * D + H * D * W + 3 * W * z["ff"]) + z["vocab"] * W
+        entry = {"config": z, "params": {}}
+        for label, cfg, costs in (("tetodra", tcfg, _model_costs(tcfg, context)), ("kaketar", kcfg, _model_costs(kcfg, context)),
+                                  ("qwen3_dense", qcfg, (q_params, 2.0 * G * D * 2 * L, 0.0))):
+            print(f"[bench] design sizes {size_name}: {label}", file=sys.stderr, flush=True)
+            params, kv, state = costs
+            r = run_model(cfg, f"{label} {size_name}", {"active": params, "read": params}, kv, state)
+            r["prefill_frac_of_measured"] = round(r["prefill_tflops"] / pk["bf16_tflops"], 4)
+            r["decode_hbm_frac_of_measured"] = round(r["decode_gbs"] / pk["hbm_gbs"], 4)
+            print(f"[bench] {r}", file=sys.stderr, flush=True)
+            entry[label] = r
+            entry["params"][label] = params
+        record["sizes"][size_name] = entry
+
+    # ---- kernels one by one at the larger sizes (L2 flushed between runs)
+    z = TETODRA_SIZES["8b"]
+    W, bf, T = z["width"], torch.bfloat16, tokens_pf
+    kern = {}
+
+    def hbm(nbytes, ms):
+        return {"us": round(ms * 1e3, 1), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)}
+
+    def tensor(flops, ms):
+        return {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1), "frac_tensor": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)}
+
+    # the scaled sum of three outputs with the layer norm, beside the sum of one output with the RMS norm
+    h = torch.randn(T * 4, W, device=device)
+    deltas = [torch.randn(T * 4, W, device=device).to(bf) for _ in range(3)]
+    scales = [torch.rand(W, device=device) for _ in range(3)]
+    gain16 = torch.ones(W, device=device, dtype=bf)
+    out = torch.empty_like(deltas[0])
+    per = h.numel()
+    kern["scaled_add_layernorm_3_outputs"] = hbm(per * (8 + 3 * 2 + 2), timed(lambda: ops.scaled_add_layernorm(h, deltas, scales, gain16, 1e-5, out)))
+    kern["scaled_add_layernorm_1_output"] = hbm(per * (8 + 2 + 2), timed(lambda: ops.scaled_add_layernorm(h, deltas[:1], scales[:1], gain16, 1e-5, out)))
+    kern["add_rmsnorm"] = hbm(per * (8 + 2 + 2), timed(lambda: ops.add_rmsnorm(h, deltas[0], gain16, 1e-5, out)))
+    del h, deltas, out
+
+    rows, page, ctx_len = 64, 16, context
+
+    def context_for(segs):
+        seg, tiles, dec, row = [], [], [], 0
+        for s, (slot, p0, n) in enumerate(segs):
+            seg.append([slot, row, n, p0])
+            if n == 1:
+                dec.append(row)
+            else:
+                tiles += [(s, off) for off in range(0, n, 64)]
+            row += n
+        tiles.sort(key=lambda t: (t[1] % 256 != 0, t[1] % 128 != 0))
+        pos = torch.tensor([p0 + i for _, p0, n in segs for i in range(n)], dtype=torch.int32, device=device)
+        slot = torch.tensor([sl for sl, _, n in segs for _ in range(n)], dtype=torch.int32, device=device)
+        return StepContext(tokens=row, token_ids=None, positions=pos, token_slot=slot, want_rows=None, segments=[],
+                           seg_info=torch.tensor(seg, dtype=torch.int32, device=device),
+                           dec_rows=None if len(dec) == row else torch.tensor(dec, dtype=torch.int32, device=device),
+                           n_dec=len(dec), pf_tiles=torch.tensor(tiles, dtype=torch.int32, device=device).view(-1, 2),
+                           n_tiles=len(tiles), n_tiles128=sum(1 for t in tiles if t[1] % 128 == 0),
+                           n_tiles256=sum(1 for t in tiles if t[1] % 256 == 0), max_context=ctx_len, max_segment=max(n for _, _, n in segs))
+
+    # attention: scores with a table of distance biases and a learned sink, and plain scores after a rotation, over
+    # two planes of the paged cache, beside Qwen3's paged attention at the same heads; a prompt of 2048 tokens, and
+    # 64 one-token rows at context 2048.  Before each, the kernel that norms, scales or turns queries and keys and
+    # writes the cache, beside Qwen3's
+    H, G, D = z["a_heads"], z["a_kv"], z["a_dim"]
+    n_pages = rows * ctx_len // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=device).view(rows, ctx_len // page).contiguous()
+    pool = (torch.randn(n_pages, 2 * G * page * D, device=device) * 0.5).to(bf)
+    k_plane = pool[:, :G * page * D].unflatten(1, (G, page, D))
+    v_plane = pool[:, G * page * D:].unflatten(1, (G, page, D))
+    kv_u = pool.view(n_pages, 2, G, page, D)
+    bias = torch.randn(H, 129, device=device)
+    sink = torch.randn(H, device=device)
+    gain = torch.ones(D, device=device, dtype=bf)
+    inv_freq = (1000000.0 ** (-torch.arange(D // 2, dtype=torch.float64) * 2 / D)).float().to(device)
+    for what, segs in (("prefill_2048", [(0, 0, T)]), ("decode_64_rows_ctx_2048", [(i, ctx_len - 1, 1) for i in range(rows)])):
+        ctx = context_for(segs)
+        n = ctx.tokens
+        q = torch.randn(n, H * D, device=device).to(bf)
+        o = torch.empty_like(q)
+        keyed_proj = torch.randn(n, (H + G) * D, device=device).to(bf)
+        full_proj = torch.randn(n, (H + 2 * G) * D, device=device).to(bf)
+        moved = n * ((H + 2 * G) * D * 2 + (H + 2 * G) * D * 2)
+        kern[f"qkv_store_keys_as_values_{what}"] = hbm(n * ((H + G) * D * 2 + (H + 2 * G) * D * 2), timed(lambda: ops.qkv_unit_store(
+            keyed_proj, q, ctx.positions, ctx.token_slot, table, k_plane, v_plane, page, H, G, D, D, 1e-5, q_gain=gain, k_gain=gain,
+            q_temperature=(0.25, 512), values_are_keys=True)))
+        kern[f"qkv_store_rotation_{what}"] = hbm(moved, timed(lambda: ops.qkv_unit_store(
+            full_proj, q, ctx.positions, ctx.token_slot, table, k_plane, v_plane, page, H, G, D, D, None, inv_freq=inv_freq, rot_dims=D)))
+        kern[f"qwen3_qk_norm_rope_store_{what}"] = hbm(moved, timed(lambda: ops.qk_norm_rope_store(
+            full_proj, gain, gain, 1e-6, inv_freq, D, ctx.positions, ctx.token_slot, table, kv_u, page, q, H, G, D,
+            ops.QK_NORM | ops.QK_ROPE | ops.QK_STORE | ops.QK_QOUT)))
+        runs = {"attention_table_sink": lambda: ops.attention_biased(q, k_plane, v_plane, ctx.positions, ctx.token_slot, table, page, H, G, D, D,
+                                                                     D ** -0.5, o, sink=True, sink_logits=sink, distance_bias=bias, ctx=ctx),
+                "attention_two_planes": lambda: ops.attention_biased(q, k_plane, v_plane, ctx.positions, ctx.token_slot, table, page, H, G, D, D,
+                                                                     D ** -0.5, o, ctx=ctx),
+                "paged_attention": lambda: ops.paged_attention(q, kv_u, ctx.positions, ctx.token_slot, table, page, H, G, D, None,
+                                                               D ** -0.5, o, ctx=ctx)}
+        for name, fn in runs.items():
+            ms = timed(fn)
+            kern[f"{name}_{what}"] = tensor(4.0 * H * D * T * (T + 1) / 2, ms) if what.startswith("prefill") else \
+                hbm(rows * ctx_len * 2 * G * D * 2, ms)
+    del pool, k_plane, v_plane, kv_u
+
+    # the recurrences on the scan kernel: 2048 tokens of one request, and 64 one-token rows (state read and written
+    # once per row): the matrix memory, the gated linear attention, the delta rule with a decay per head, and
+    # Kaketar's delta rule with a decay per channel
+    Hm, mk, mv = z["m_heads"], z["m_dim"], z["m_vdim"]
+    Hd, Gd, dk, dv, taps = z["d_heads"], z["d_kv"], z["d_dim"], z["d_vdim"], z["taps"]
+
+    def scan_record(n, ms, heads, k, v, io, work, state_words):
+        total = io + work + (0 if n == T else 2 * rows * state_words * 4)
+        return {"us": round(ms * 1e3, 1), "tokens_per_s": round(n / ms * 1e3, 1),
+                "gflops_fp32": round(6.0 * n * heads * k * v / ms / 1e6, 1), "gbs": round(total / ms / 1e6, 1),
+                "frac_hbm": round(total / ms / 1e6 / pk["hbm_gbs"], 3)}
+
+    for what, n, seg in (("prefill_2048", T, [[0, 0, T, 0]]), ("decode_64_rows", rows, None)):
+        slots = torch.zeros(n, dtype=torch.int32, device=device) if seg else torch.arange(n, dtype=torch.int32, device=device)
+        seg_info = torch.tensor(seg, dtype=torch.int32, device=device) if seg else None
+        # matrix memory and gated linear attention
+        proj = torch.randn(n, Hm * (2 * mk + 2 * mv), device=device).to(bf)
+        gate = proj[:, Hm * (2 * mk + mv):]
+        for kind, zc, p0, per_head, act in (("log_gates", 2 * Hm, 12.0, True, "sigmoid"), ("channel_decay", Hm * mk, 1.0 / 8, False, "silu")):
+            words = ops.linear_recurrence_state_floats(kind, Hm, mk, mv)
+            state = torch.zeros(rows, words, device=device)
+            zz = torch.randn(n, zc, device=device)
+            zb = torch.randn(zc, device=device) + 3.0
+            weight = torch.ones(Hm * mv if per_head else mv, device=device)
+            ms = timed(lambda: ops.linear_recurrence(proj, kind, zz, zb, p0, gate, act, weight, per_head, 1e-5, slots, seg_info, state,
+                                                     Hm, mk, mv, mk ** -0.5, bf))
+            io = n * (Hm * (2 * mk + 2 * mv) * 2 + zc * 4 + Hm * mv * 2)
+            work = n * (3 * Hm * mk + 2 * Hm * (mv + 1)) * 4 * 2
+            name = "matrix_memory" if kind == "log_gates" else "gated_linear_attention"
+            kern[f"{name}_{what}"] = scan_record(n, ms, Hm, mk, mv, io, work, words)
+            del state
+        # the two delta rules
+        for name, G2, per_head in (("delta_rule_decay_per_head", Gd, True), ("kaketar_delta_rule_decay_per_channel", Hd, False)):
+            channels = 2 * G2 * dk + Hd * dv
+            words = ops.delta_rule_state_floats(Hd, G2, dk, dv, taps)
+            state = torch.zeros(rows, words, device=device)
+            conv_w = (torch.randn(channels, taps, device=device) * 0.5).to(bf)
+            conv_t = conv_w.t().contiguous()
+            proj = torch.randn(n, (channels + Hd + 7) // 8 * 8, device=device).to(bf)
+            a = torch.randn(n, Hd if per_head else Hd * dk, device=device)
+            dt_bias = torch.randn(Hd if per_head else Hd * dk, device=device) - 4.0
+            rate = torch.ones(Hd, device=device)
+            gate = torch.randn(n, Hd * dv, device=device).to(bf)
+            weight = torch.ones(dv, device=device)
+            ms = timed(lambda: ops.delta_rule(proj, conv_w, taps, a, dt_bias, rate, gate, weight, 1e-5, slots, seg_info, state,
+                                              Hd, G2, dk, dv, dk ** -0.5, 1e-6, bf, conv_t=conv_t, decay_per_head=per_head,
+                                              gate_act="silu" if per_head else "sigmoid"))
+            io = n * ((channels + Hd) * 2 + a.shape[1] * 4 + Hd * dv * 2 + Hd * dv * 2)
+            work = n * (2 * G2 * dk + 2 * Hd * dv + Hd * dk + Hd) * 4 * 2
+            kern[f"{name}_{what}"] = scan_record(n, ms, Hd, dk, dv, io, work, words)
+            del state
+    ops.check_error_word(device)
+    record["kernels"] = kern
+    clock_record = clocks.stop(windows)
+    first = record["sizes"][sorted(record["sizes"])[0]]["tetodra"]
+    print(json.dumps({"metric": f"decode tok/s @ batch {batch} (Tetodra design sizes, context {context}, 1 B200)",
+                      "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "ms_per_step": first["decode_ms"], "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "design": "tetodra", "clocks": clock_record, "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},
+                      **record}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -895,7 +1145,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--model", default="8b", choices=sorted(set(MODELS) | set(DESIGN_SIZES)),
+    ap.add_argument("--model", default="8b", choices=sorted(set(MODELS) | set(DESIGN_SIZES) | set(TETODRA_SIZES)),
                     help="the sizes: 8b is the benchmark configuration, 0.6b and 32b the other two the reference is quoted on")
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (named in the record) if memory or time needs it")
@@ -908,7 +1158,7 @@ def main() -> int:
     ap.add_argument("--skip-check", action="store_true", help="leave out the logits check before the timed phases")
     ap.add_argument("--ref-all", action="store_true",
                     help="reference arm: its model_main --bench at batch 1, 8 and 64 instead of --batch alone")
-    ap.add_argument("--design", default=None, choices=["panolorn", "kaketar"],
+    ap.add_argument("--design", default=None, choices=["panolorn", "kaketar", "tetodra"],
                     help="instead of the default workload: this design's prefill and decode throughput at sizes that "
                          "resemble a real model's layers beside Qwen3 dense at equal sizes, and its kernels one by one")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e", "mixed", "p128"],
@@ -918,7 +1168,7 @@ def main() -> int:
         if args.gpus != 1 or args.impl != "ours":
             print("bench.py: --design runs this engine on one GPU")
             return 2
-        return kaketar_bench(args) if args.design == "kaketar" else design_bench(args)
+        return {"kaketar": kaketar_bench, "tetodra": tetodra_bench}.get(args.design, design_bench)(args)
     if args.model not in MODELS:
         ap.error(f"--model {args.model} goes with --design")
     model_name, model_sizes = MODELS[args.model]
