@@ -54,12 +54,16 @@ def make_ctx(rows):
         else:
             tiles += [[s, off] for off in range(0, n, 64)]
         row += n
+    # blocks at multiples of 256 rows first, then those at other multiples of 128 (the tcgen05 kernel's lists)
+    tiles.sort(key=lambda t: (t[1] % 256 != 0, t[1] % 128 != 0, -(rows[t[0]][1] + t[1])))
     i32 = dict(dtype=torch.int32, device=DEV)
     return StepContext(tokens=row, token_ids=None, positions=torch.tensor(pos, **i32),
                        token_slot=torch.tensor(slots, **i32), want_rows=None, segments=[],
                        seg_info=torch.tensor(seg, **i32),
                        dec_rows=torch.tensor(dec, **i32) if dec and len(dec) < row else None, n_dec=len(dec),
                        pf_tiles=torch.tensor(tiles, **i32).view(-1, 2), n_tiles=len(tiles),
+                       n_tiles128=sum(1 for t in tiles if t[1] % 128 == 0),
+                       n_tiles256=sum(1 for t in tiles if t[1] % 256 == 0),
                        decode_only=all(n == 1 for _, _, n in rows), max_context=max(p0 + n for _, p0, n in rows),
                        max_segment=max(n for _, _, n in rows))
 
@@ -279,6 +283,69 @@ def test_attention_with_a_rotation_of_part_of_the_head(case, dtype):
     # the angles are the positions': a request that starts later in the cache's numbering would differ
     moved = plain.rotate_half(torch.ones(1, 1, dk, dtype=F64), torch.tensor([257]), case["base"], case["dims"])
     assert (moved - 1).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("splits_forced", [None, 1])
+@pytest.mark.parametrize("H,G,table_rows,sink", [(4, 2, 300, True), (3, 3, 64, True), (2, 1, 1500, False), (2, 2, 0, False)])
+def test_planes_attention_on_tcgen05_over_a_long_request(H, G, table_rows, sink, splits_forced, monkeypatch):
+    """Width 128 on both sides: prompt portions take the tcgen05 kernel over the two planes.  One portion of 2500
+    tokens behind 900 in the cache (the rings of tiles and every barrier wrap; few blocks, so the keys of a block
+    are shared out and summed again), with a table of biases whose end falls inside a tile, a sink, and one key
+    900 or more tokens back made to stand out for sampled rows.  Against float64 and against the mma.sync kernel."""
+    from tiny_llm_infer_b200 import ops
+    d, page, have, new = 128, 16, 900, 2500
+    n, pages = have + new, -(-(have + new) // page)
+    g = torch.Generator().manual_seed(H * 10 + G)
+    flat = (torch.randn(pages + 5, 2 * G * page * d, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    k_plane = flat[:, :G * page * d].unflatten(1, (G, page, d))
+    v_plane = flat[:, G * page * d:].unflatten(1, (G, page, d))
+    table = torch.randperm(pages + 5, generator=g)[:pages].to(torch.int32).view(1, -1).to(DEV)
+    q = (torch.randn(new, H, d, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    keys_of = lambda plane: plane[table[0].long()].double().permute(1, 0, 2, 3).reshape(G, pages * page, d)[:, :n]
+    K, V = keys_of(k_plane), keys_of(v_plane)
+    sample = torch.cat([torch.arange(0, new, 41), torch.tensor([127, 128, 255, 256, new - 1])])
+    for i, r in enumerate(sample.tolist()):                   # a far key that carries the answer of these rows
+        q[r, :, :] = (K[:, (7 * i) % have].repeat_interleave(H // G, 0) * 4.0).to(torch.bfloat16)
+    bias = sinks = None
+    if table_rows:
+        bias = (torch.randn(H, table_rows, generator=g) * 1.5).to(DEV)
+        bias[:, -1] = 2.0                                      # what the far keys get
+    if sink:
+        sinks = (torch.randn(H, generator=g) * 2.0 + 4.0).to(DEV)
+    ctx = make_ctx([(0, have, new)])
+    if splits_forced:
+        monkeypatch.setattr(ops, "prefill_splits", lambda blocks, ctx_len: splits_forced)
+    else:
+        pairs = ops.prefill_tcgen05_block_rows(H, G) == 128
+        assert ops.prefill_splits(ctx.n_tiles128 * H // 2 if pairs else ctx.n_tiles256 * H, n) > 1
+    outs = {}
+    for fast in (True, False):
+        monkeypatch.setattr(ops, "PREFILL_TCGEN05", fast)
+        before = ops.tcgen05_calls
+        out = torch.zeros(new, H * d, dtype=torch.bfloat16, device=DEV)
+        ops.attention_biased(q.view(new, -1), k_plane, v_plane, ctx.positions, ctx.token_slot, table, page, H, G, d, d,
+                             0.11, out, sink=sink, sink_logits=sinks, distance_bias=bias, ctx=ctx)
+        ops.check_error_word(torch.device(DEV))
+        assert (ops.tcgen05_calls > before) == fast
+        outs[fast] = out.double().view(new, H, d)
+    pos = have + sample.to(DEV)
+    keys = torch.arange(n, device=DEV)
+    mask = keys[None, :] <= pos[:, None]
+    for h in range(H):
+        s = q[sample.to(DEV), h].double() @ K[h // (H // G)].T * 0.11
+        if bias is not None:
+            s = s + bias[h].double()[(pos[:, None] - keys[None, :]).clamp(0, table_rows - 1)]
+        s = s.masked_fill(~mask, float("-inf"))
+        top = s.max(-1, keepdim=True).values
+        e = torch.exp(s - top)
+        den = e.sum(-1, keepdim=True) + (torch.exp(sinks[h].double() - top) if sink else 0.0)
+        want = (e / den) @ V[h // (H // G)]
+        # the far key holds most of the weight of its row
+        assert (e / den)[torch.arange(len(sample)), [(7 * i) % have for i in range(len(sample))]].min() > 0.3
+        for fast in (True, False):
+            err = (outs[fast][sample.to(DEV), h] - want).abs().max().item()
+            assert err < 0.02 * want.abs().max().item() + 0.01, (h, fast, err)
+    assert (outs[True] - outs[False]).abs().max() < 0.03
 
 
 # ----------------------------------------------------------------------------- the three recurrences as parts

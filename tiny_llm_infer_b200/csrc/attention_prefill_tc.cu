@@ -57,6 +57,7 @@ constexpr int kThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRaise = 8.0f;                    // the reference maximum follows only beyond 2^8
 constexpr int kSpinLimit = 1 << 20;
+constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t sa(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -182,11 +183,20 @@ struct QTile {
     int head, q_off, rows, first_pos, last_pos, kt_first, n;
 };
 
+// Keys and values lie in planes of their own: row (page * rows_per_page + head * page_size + place in the
+// page) of 128 elements from `k_base` and from `v_base` (the two halves of a page of the plain cache, or two
+// views into pages that hold more).  kBias: `dist_bias` [q_heads][dist_len] float32 is added to the scaled
+// score by the distance from the query to the key (distances from dist_len - 1 on share the last entry).
+// `sink_logit` (or null): exp(sink_logit[head]) joins the softmax's denominator, once, with no value.
+template <bool kBias>
 __global__ void __launch_bounds__(kThreads, 1)
-paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const bf16* __restrict__ cache,
+paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const bf16* __restrict__ k_base,
+                                  const bf16* __restrict__ v_base, int rows_per_page,
                                   const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                   const int* __restrict__ block_table, int max_pages, int page_size, int q_heads,
                                   int kv_heads, int window, float scale_log2e, int pair_heads,
+                                  const float* __restrict__ dist_bias, int dist_len,
+                                  const float* __restrict__ sink_logit,
                                   bf16* __restrict__ out, int splits, float* __restrict__ part_o,
                                   float* __restrict__ part_ml, int* __restrict__ error_word) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -381,14 +391,14 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         // shuffle; the 32 after them are fetched while these are in use.
         const int w = warp - 2;
         const int* table = block_table + (size_t)slot * max_pages;
-        const char* cache_b = reinterpret_cast<const char*>(cache);
-        const int v_off = kv_heads * page_size;              // from a key's row to its value's
+        const char* const k_b = reinterpret_cast<const char*>(k_base);
+        const char* const v_b = reinterpret_cast<const char*>(v_base);
         auto lookup = [&](int chunk) -> int {                // row of K of this lane's group, -1: none
             const int idx = chunk * 32 + lane;
             const int key0 = ((kt_lo + (idx >> 1)) * 4 + w * 2 + (idx & 1)) * 16;
             if (key0 > last_pos) return -1;
             const int page = table[key0 / page_size];
-            return page < 0 ? -1 : (int)(((long long)page * 2 * kv_heads + g) * page_size + key0 % page_size);
+            return page < 0 ? -1 : (int)((long long)page * rows_per_page + g * page_size + key0 % page_size);
         };
         int rows0 = lookup(0), rows1 = -1;                   // chunks of even and odd number
         auto copy_tile = [&](int j, int value, uint32_t dst) {
@@ -399,8 +409,9 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int in_grp = 2 * i + (lane >> 4), key = w * 32 + h * 16 + in_grp, c = lane & 15;
-                    const long long row = (long long)base + in_grp + (value ? v_off : 0);
-                    const char* src = base < 0 ? cache_b : cache_b + row * (kHD * 2) + c * 16;
+                    const long long row = (long long)base + in_grp;
+                    const char* const plane = value ? v_b : k_b;
+                    const char* src = base < 0 ? plane : plane + row * (kHD * 2) + c * 16;
                     const uint32_t d = dst + (c >> 3) * (kKBytes / 2) + key * 128 + (((c & 7) ^ (key & 7)) << 4);
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src),
                                  "r"(base < 0 ? 0 : 16)
@@ -453,6 +464,12 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         uint64_t* const o_full = &bars->o_full[x];
         float m_ref = -INFINITY, l_run = 0.0f;
         bool alive = t.n > 0 && !*aborted;
+        const float* bias_row = nullptr;                      // this head's biases by distance
+        float bias_far = 0.0f;                                // the last one, times log2(e)
+        if constexpr (kBias) {
+            bias_row = dist_bias + (size_t)t.head * dist_len;
+            bias_far = bias_row[dist_len - 1] * kLog2e;
+        }
         for (int j = 0; j < t.n && alive; ++j) {
             const uint32_t t_s = tmem_sx + (j & 1) * kBN;
             if (!mbar_wait(&bars->s_full[x][j & 1], (j >> 1) & 1)) {
@@ -466,6 +483,22 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             tmem_ld32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
             tmem_ld_wait();
             const int key0 = (t.kt_first + j) * kBN;
+            if constexpr (kBias) {
+                // from here on sv holds (score * scale + bias) * log2(e).  A tile all of whose keys lie
+                // dist_len - 1 or more behind the block's first row has one bias for all scores.
+                if (t.first_pos - (key0 + kBN - 1) >= dist_len - 1) {
+#pragma unroll
+                    for (int i = 0; i < kBN; ++i)
+                        sv[i] = __float_as_uint(fmaf(__uint_as_float(sv[i]), scale_log2e, bias_far));
+                } else {
+                    const int d0 = pos - key0;                // the distance to key i of the tile is d0 - i
+#pragma unroll
+                    for (int i = 0; i < kBN; ++i) {
+                        const float b = __ldg(bias_row + min(max(d0 - i, 0), dist_len - 1));
+                        sv[i] = __float_as_uint(fmaf(b, kLog2e, __uint_as_float(sv[i]) * scale_log2e));
+                    }
+                }
+            }
             // only tiles on the diagonal or at the window's far edge hold keys some row may not see
             if (key0 + kBN - 1 > t.first_pos || (window > 0 && key0 < t.last_pos - window + 1)) {
 #pragma unroll
@@ -477,7 +510,7 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < kBN; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sv[i]));
-            const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
+            const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * (kBias ? 1.0f : scale_log2e);
             // raise the reference maximum only when this tile is far above it
             const bool raise = tile_max > m_ref + kRaise;
             float factor = 1.0f;
@@ -512,8 +545,9 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             uint32_t pw[kBN / 2];
 #pragma unroll
             for (int i = 0; i < kBN; i += 2) {
-                const float a = ex2(fmaf(__uint_as_float(sv[i]), scale_log2e, -m_use));
-                const float b = ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2e, -m_use));
+                const float a = ex2(kBias ? __uint_as_float(sv[i]) - m_use : fmaf(__uint_as_float(sv[i]), scale_log2e, -m_use));
+                const float b = ex2(kBias ? __uint_as_float(sv[i + 1]) - m_use
+                                          : fmaf(__uint_as_float(sv[i + 1]), scale_log2e, -m_use));
                 sum[(i >> 1) & 3] += a + b;
                 pw[i >> 1] = pack2(a, b);
             }
@@ -557,6 +591,7 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             }
         } else if (finish) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (sink_logit != nullptr) l_run += ex2(sink_logit[t.head] * kLog2e - m_ref);   // every row has seen a key
             const float inv = 1.0f / l_run;
             const uint32_t stage = q_s + x * kQBytes, stage_row = stage + r * 256;
 #pragma unroll 1
@@ -605,7 +640,8 @@ constexpr int kCombineRows = 8;
 __global__ void paged_attention_prefill_combine_kernel(const float* part_o, const float* part_ml,
                                                        const int* __restrict__ seg_info,
                                                        const int* __restrict__ tiles, int rows_per_tile,
-                                                       int q_heads, int splits, bf16* __restrict__ out) {
+                                                       int q_heads, int splits, const float* __restrict__ sink_logit,
+                                                       bf16* __restrict__ out) {
     const int seg = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1], head = blockIdx.y, d = threadIdx.x;
     const int start = seg_info[4 * seg + 1], len = seg_info[4 * seg + 2];
     for (int i = 0; i < kCombineRows; ++i) {
@@ -622,6 +658,7 @@ __global__ void paged_attention_prefill_combine_kernel(const float* part_o, cons
             total += part_ml[(base + z) * 2 + 1] * f;
             acc += part_o[(base + z) * kHD + d] * f;
         }
+        if (sink_logit != nullptr) total += exp2f(sink_logit[head] * kLog2e - mm);
         out[((size_t)(start + r) * q_heads + head) * kHD + d] = __float2bfloat16_rn(acc / total);
     }
 }
@@ -666,6 +703,58 @@ extern "C" int tllm_paged_attention_prefill_tc_rows(int q_heads, int kv_heads) {
     return (kv_heads > 0 && q_heads % kv_heads == 0 && (q_heads / kv_heads) % 2 == 0) ? 128 : 256;
 }
 
+// The launch behind both entry points below.
+static int launch_prefill_tc(const char* name, const void* q, int tokens, const void* k_base, const void* v_base,
+                             long long rows_per_page, long long kv_rows, const int* seg_info, const int* tiles,
+                             int n_tiles, const int* block_table, int max_pages, int page_size, int q_heads,
+                             int kv_heads, int window, float scale, const float* dist_bias, int dist_len,
+                             const float* sink_logit, void* out, int splits, float* part_o, float* part_ml,
+                             int* error_word, cudaStream_t stream) {
+    TLLM_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads <= 65535,
+                 "%s: %d query heads over %d key/value heads", name, q_heads, kv_heads);
+    TLLM_REQUIRE(page_size > 0 && page_size % 16 == 0, "%s: page size %d is no multiple of 16", name, page_size);
+    TLLM_REQUIRE(error_word != nullptr && n_tiles >= 0 && n_tiles <= 65535 && tokens > 0,
+                 "%s: bad arguments (at most 65535 blocks of query rows)", name);
+    TLLM_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (part_o != nullptr && part_ml != nullptr)),
+                 "%s: %d splits (1 to 64; more than one needs scratch)", name, splits);
+    TLLM_REQUIRE(kv_rows < (1ll << 31), "%s: a cache of %lld rows exceeds the kernel's 32-bit row index", name, kv_rows);
+    TLLM_REQUIRE(dist_bias == nullptr || dist_len > 0, "%s: an empty table of biases", name);
+    if (n_tiles == 0) return 0;
+    TLLM_REQUIRE((reinterpret_cast<uintptr_t>(k_base) & 15u) == 0 && (reinterpret_cast<uintptr_t>(v_base) & 15u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(part_o) & 15u) == 0,
+                 "%s: pointers must be 16-byte aligned", name);
+    CUtensorMap mq;
+    TLLM_REQUIRE(pftc::make_map(&mq, q, tokens, (long long)q_heads * 128, 128),
+                 "%s: cuTensorMapEncodeTiled failed or is not available", name);
+    static OncePerDevice configured;
+    if (configured.first()) {
+        cudaError_t e = cudaFuncSetAttribute(pftc::paged_attention_prefill_tc_kernel<false>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, pftc::kSmemBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(pftc::paged_attention_prefill_tc_kernel<true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, pftc::kSmemBytes);
+        if (e != cudaSuccess) { set_error("%s: %s", name, cudaGetErrorString(e)); return (int)e; }
+        configured.done();
+    }
+    const int rows_per_tile = tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads);
+    const int pair_heads = rows_per_tile == 128;
+    const dim3 grid(pair_heads ? q_heads / 2 : q_heads, n_tiles, splits);
+#define PFTC(BIAS)                                                                                                \
+    pftc::paged_attention_prefill_tc_kernel<BIAS><<<grid, pftc::kThreads, pftc::kSmemBytes, stream>>>(            \
+        mq, (const bf16*)k_base, (const bf16*)v_base, (int)rows_per_page, seg_info, tiles, block_table, max_pages, \
+        page_size, q_heads, kv_heads, window, scale * pftc::kLog2e, pair_heads, dist_bias, dist_len, sink_logit,  \
+        (bf16*)out, splits, part_o, part_ml, error_word)
+    if (dist_bias != nullptr) PFTC(true);
+    else PFTC(false);
+#undef PFTC
+    int rc = finish_launch(name);
+    if (rc != 0 || splits == 1) return rc;
+    pftc::paged_attention_prefill_combine_kernel<<<dim3(n_tiles, q_heads, rows_per_tile / pftc::kCombineRows), 128, 0, stream>>>(
+        part_o, part_ml, seg_info, tiles, rows_per_tile, q_heads, splits, sink_logit, (bf16*)out);
+    return finish_launch("paged_attention_prefill_combine");
+}
+
 // tiles: int[n_tiles][2] = segment, offset of the block's first query row; the offsets are the
 // multiples of tllm_paged_attention_prefill_tc_rows() below the segment's length.
 // q [tokens, q_heads * 128], cache [num_pages, 2, kv_heads, page_size, 128], both bfloat16.
@@ -678,40 +767,28 @@ extern "C" int tllm_paged_attention_prefill_tc(
     const int* block_table, int max_pages, int page_size, int q_heads, int kv_heads, int head_dim, int window,
     float scale, void* out, int splits, float* part_o, float* part_ml, int* error_word, cudaStream_t stream) {
     TLLM_REQUIRE(head_dim == 128, "paged_attention_prefill_tc: head_dim %d is not 128", head_dim);
-    TLLM_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads <= 65535,
-                 "paged_attention_prefill_tc: %d query heads over %d key/value heads", q_heads, kv_heads);
-    TLLM_REQUIRE(page_size > 0 && page_size % 16 == 0, "paged_attention_prefill_tc: page size %d is no multiple of 16",
-                 page_size);
-    TLLM_REQUIRE(error_word != nullptr && n_tiles >= 0 && n_tiles <= 65535 && tokens > 0,
-                 "paged_attention_prefill_tc: bad arguments (at most 65535 blocks of query rows)");
-    TLLM_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (part_o != nullptr && part_ml != nullptr)),
-                 "paged_attention_prefill_tc: %d splits (1 to 64; more than one needs scratch)", splits);
-    const long long kv_rows = (long long)num_pages * 2 * kv_heads * page_size;
-    TLLM_REQUIRE(kv_rows < (1ll << 31), "paged_attention_prefill_tc: a cache of %lld rows exceeds the kernel's 32-bit row index",
-                 kv_rows);
-    if (n_tiles == 0) return 0;
-    TLLM_REQUIRE((reinterpret_cast<uintptr_t>(cache) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q) & 15u) == 0 &&
-                     (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && (reinterpret_cast<uintptr_t>(part_o) & 15u) == 0,
-                 "paged_attention_prefill_tc: pointers must be 16-byte aligned");
-    CUtensorMap mq;
-    TLLM_REQUIRE(pftc::make_map(&mq, q, tokens, (long long)q_heads * 128, 128),
-                 "paged_attention_prefill_tc: cuTensorMapEncodeTiled failed or is not available");
-    static OncePerDevice configured;
-    if (configured.first()) {
-        cudaError_t e = cudaFuncSetAttribute(pftc::paged_attention_prefill_tc_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, pftc::kSmemBytes);
-        if (e != cudaSuccess) { set_error("paged_attention_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
-        configured.done();
-    }
-    const int rows_per_tile = tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads);
-    const int pair_heads = rows_per_tile == 128;
-    pftc::paged_attention_prefill_tc_kernel<<<dim3(pair_heads ? q_heads / 2 : q_heads, n_tiles, splits), pftc::kThreads,
-                                              pftc::kSmemBytes, stream>>>(
-        mq, (const bf16*)cache, seg_info, tiles, block_table, max_pages, page_size, q_heads, kv_heads, window,
-        scale * 1.4426950408889634f, pair_heads, (bf16*)out, splits, part_o, part_ml, error_word);
-    int rc = finish_launch("paged_attention_prefill_tc");
-    if (rc != 0 || splits == 1) return rc;
-    pftc::paged_attention_prefill_combine_kernel<<<dim3(n_tiles, q_heads, rows_per_tile / pftc::kCombineRows), 128, 0, stream>>>(
-        part_o, part_ml, seg_info, tiles, rows_per_tile, q_heads, splits, (bf16*)out);
-    return finish_launch("paged_attention_prefill_combine");
+    const long long rows_per_page = 2ll * kv_heads * page_size;
+    return launch_prefill_tc("paged_attention_prefill_tc", q, tokens, cache,
+                             (const bf16*)cache + (size_t)kv_heads * page_size * 128, rows_per_page,
+                             (long long)num_pages * rows_per_page, seg_info, tiles, n_tiles, block_table, max_pages,
+                             page_size, q_heads, kv_heads, window, scale, nullptr, 0, nullptr, out, splits, part_o,
+                             part_ml, error_word, stream);
+}
+
+// The same kernel over keys and values in planes of their own, [pages, kv_heads, page_size, 128] views whose
+// pages lie `page_stride` elements apart (a multiple of 128), with the two changes of the score the kernel
+// knows: dist_bias [q_heads, dist_len] float32 added by distance (or null) and a learned sink per query head
+// (or null).  Widths of 128 for keys and values only.
+extern "C" int tllm_attention_planes_prefill_tc(
+    const void* q, int tokens, const void* k_plane, const void* v_plane, long long page_stride, int num_pages,
+    const int* seg_info, const int* tiles, int n_tiles, const int* block_table, int max_pages, int page_size,
+    int q_heads, int kv_heads, int window, float scale, const float* dist_bias, int dist_len,
+    const float* sink_logit, void* out, int splits, float* part_o, float* part_ml, int* error_word,
+    cudaStream_t stream) {
+    TLLM_REQUIRE(page_stride > 0 && page_stride % 128 == 0,
+                 "attention_planes_prefill_tc: pages %lld elements apart (no multiple of 128)", page_stride);
+    return launch_prefill_tc("attention_planes_prefill_tc", q, tokens, k_plane, v_plane, page_stride / 128,
+                             (long long)num_pages * (page_stride / 128), seg_info, tiles, n_tiles, block_table,
+                             max_pages, page_size, q_heads, kv_heads, window, scale, dist_bias, dist_len, sink_logit,
+                             out, splits, part_o, part_ml, error_word, stream);
 }

@@ -250,8 +250,10 @@ __global__ void scaled_add_layernorm_kernel(float* h, ScaledDeltas ds, const TG*
         dst[i] = from_f32<TO>(to_f32<TG>(gain[i]) * (ln_row[i] - mean) * scale);
 }
 
-// Vector form: the row stays in registers, CHUNKS groups of eight elements per thread.
-template <typename TD, typename TG, typename TO, int CHUNKS>
+// Vector form: the row stays in registers, CHUNKS groups of eight elements per thread.  The number of outputs N
+// is a compile-time constant, so that a chunk's loads (the stream, N outputs, N scale vectors) are all in flight
+// before the first sum.
+template <typename TD, typename TG, typename TO, int CHUNKS, int N>
 __global__ void scaled_add_layernorm_vec_kernel(float* h, ScaledDeltas ds, const TG* __restrict__ gain, float eps,
                                                 TO* __restrict__ out, const int* __restrict__ rows, int width) {
     __shared__ float scratch[32];
@@ -266,7 +268,7 @@ __global__ void scaled_add_layernorm_vec_kernel(float* h, ScaledDeltas ds, const
         return;
     }
     float* hr = h + (size_t)r * width;
-    const bool write_back = rows == nullptr && ds.n > 0;
+    const bool write_back = rows == nullptr && N > 0;
     float v[CHUNKS][8];
     float sum = 0.0f;
 #pragma unroll
@@ -274,12 +276,16 @@ __global__ void scaled_add_layernorm_vec_kernel(float* h, ScaledDeltas ds, const
         const int c = threadIdx.x + j * blockDim.x;
         if (c < n_chunks) {
             Vec8<float>::load(hr + c * 8, v[j]);
-            for (int k = 0; k < ds.n; ++k) {
-                float d[8], s[8];
-                Vec8<TD>::load((const TD*)ds.d[k] + (size_t)r * width + c * 8, d);
-                Vec8<float>::load(ds.s[k] + c * 8, s);
+            float d[N > 0 ? N : 1][8], s[N > 0 ? N : 1][8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[j][e] += s[e] * d[e];
+            for (int k = 0; k < N; ++k) {
+                Vec8<TD>::load((const TD*)ds.d[k] + (size_t)r * width + c * 8, d[k]);
+                Vec8<float>::load(ds.s[k] + c * 8, s[k]);
+            }
+#pragma unroll
+            for (int k = 0; k < N; ++k) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[j][e] += s[k][e] * d[k][e];
             }
             if (write_back) Vec8<float>::store(hr + c * 8, v[j]);
 #pragma unroll
@@ -772,13 +778,22 @@ static int launch_scaled_layernorm_typed(float* h, const ScaledDeltas& ds, const
         int block = 64;
         while (block < 1024 && block < chunks) block *= 2;
         const int per_thread = (chunks + block - 1) / block;
-#define VEC_LAUNCH(C)                                                                                         \
-    launch_pdl(kPdlNorm, scaled_add_layernorm_vec_kernel<TD, TG, TO, C>, dim3(n_out), dim3(block), 0, stream, \
+#define VEC_LAUNCH_N(C, N)                                                                                       \
+    launch_pdl(kPdlNorm, scaled_add_layernorm_vec_kernel<TD, TG, TO, C, N>, dim3(n_out), dim3(block), 0, stream, \
                h, ds, (const TG*)gain, eps, (TO*)out, rows, width)
-        if (per_thread <= 1) VEC_LAUNCH(1);
-        else if (per_thread <= 2) VEC_LAUNCH(2);
-        else VEC_LAUNCH(4);
+#define VEC_LAUNCH(C)                                            \
+    switch (ds.n) {                                              \
+        case 0: VEC_LAUNCH_N(C, 0); break;                       \
+        case 1: VEC_LAUNCH_N(C, 1); break;                       \
+        case 2: VEC_LAUNCH_N(C, 2); break;                       \
+        case 3: VEC_LAUNCH_N(C, 3); break;                       \
+        default: VEC_LAUNCH_N(C, 4); break;                      \
+    }
+        if (per_thread <= 1) { VEC_LAUNCH(1) }
+        else if (per_thread <= 2) { VEC_LAUNCH(2) }
+        else { VEC_LAUNCH(4) }
 #undef VEC_LAUNCH
+#undef VEC_LAUNCH_N
     } else {
         const size_t smem = (size_t)width * sizeof(float);
         if (smem > 48 * 1024) {

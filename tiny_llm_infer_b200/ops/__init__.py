@@ -115,6 +115,8 @@ def _declare(h) -> None:
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
         "tllm_paged_attention_prefill_tc": [vp, i32, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                             vp, i32, vp, vp, vp, vp],
+        "tllm_attention_planes_prefill_tc": [vp, i32, vp, vp, ctypes.c_longlong, i32, vp, vp, i32, vp, i32, i32,
+                                             i32, i32, i32, f32, vp, i32, vp, vp, i32, vp, vp, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(h, name)
@@ -726,6 +728,11 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
     mods = (float(scale), float(softcap or 0.0), int(chunk or 0), int(window or 0), int(bool(sink)), _p(slopes),
             _p(sink_logits), _p(distance_bias), dist_len, v_row, gate_ptr, gate_stride)
     consts = mods + (_p(out), _stream())
+    # the plain score, or one changed only by a table of biases and a learned sink, at width 128 on both
+    # sides: prompt portions go to the tcgen05 kernel of the plain cache, which reads the two planes
+    tcgen05 = PREFILL_TCGEN05 and dk == 128 and dv == 128 and not values_in_keys and not softcap and not chunk \
+        and slopes is None and gate is None and (sink_logits is not None or not sink) \
+        and page_size % 16 == 0 and stride % 128 == 0 and q_heads <= 65535
     if BIASED_FAST and ctx is not None and ctx.pf_tiles is not None and ctx.tokens == tokens \
             and q.dtype == torch.bfloat16 and gate_stride % 2 == 0 and v_row % 8 == 0 \
             and lib().tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv):
@@ -740,7 +747,24 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
                 _p(q), kp, vp, stride, _p(positions), _p(token_slot), _p(ctx.dec_rows), ctx.n_dec, _p(block_table),
                 block_table.shape[1], page_size, q_heads, kv_heads, dk, dv, *mods, splits, _p(part), _p(out), _stream()),
                 "attention_biased_decode", kernels=2 if splits > 1 else 1)
-        if ctx.n_tiles:
+        if ctx.n_tiles and tcgen05 and getattr(ctx, "n_tiles256", 0):
+            pairs = prefill_tcgen05_block_rows(q_heads, kv_heads) == 128
+            blocks = ctx.n_tiles128 if pairs else ctx.n_tiles256
+            keys = ctx.max_context if not window else min(ctx.max_context, window + 256)
+            splits = prefill_splits(blocks * (q_heads // 2 if pairs else q_heads), keys)
+            part_o = part_ml = None
+            if splits > 1:
+                n = tokens * q_heads * splits
+                ws = workspace(q.device, n * (dv + 2))
+                part_o, part_ml = ws[:n * dv], ws[n * dv:n * (dv + 2)]
+            global tcgen05_calls
+            tcgen05_calls += 1
+            _check(lib().tllm_attention_planes_prefill_tc(
+                _p(q), tokens, kp, vp, stride, k_plane.shape[0], _p(ctx.seg_info), _p(ctx.pf_tiles), blocks,
+                _p(block_table), block_table.shape[1], page_size, q_heads, kv_heads, int(window or 0), float(scale),
+                _p(distance_bias), dist_len, _p(sink_logits), _p(out), splits, _p(part_o), _p(part_ml),
+                _p(error_word(q.device)), _stream()), "attention_planes_prefill_tc", kernels=2 if splits > 1 else 1)
+        elif ctx.n_tiles:
             _check(lib().tllm_attention_biased_prefill(
                 _p(q), kp, vp, stride, _p(ctx.seg_info), _p(ctx.pf_tiles), ctx.n_tiles, _p(block_table),
                 block_table.shape[1], page_size, q_heads, kv_heads, dk, dv, *consts), "attention_biased_prefill")
