@@ -341,7 +341,8 @@ def test_planes_attention_on_tcgen05_over_a_long_request(H, G, table_rows, sink,
         den = e.sum(-1, keepdim=True) + (torch.exp(sinks[h].double() - top) if sink else 0.0)
         want = (e / den) @ V[h // (H // G)]
         # the far key holds most of the weight of its row
-        assert (e / den)[torch.arange(len(sample)), [(7 * i) % have for i in range(len(sample))]].min() > 0.3
+        held = (e / den)[torch.arange(len(sample)), [(7 * i) % have for i in range(len(sample))]]
+        assert held.median() > 0.9 and held.min() > 0.05
         for fast in (True, False):
             err = (outs[fast][sample.to(DEV), h] - want).abs().max().item()
             assert err < 0.02 * want.abs().max().item() + 0.01, (h, fast, err)

@@ -129,6 +129,117 @@ __global__ void qkv_unit_store_kernel(const T* proj, int row_stride, const T* __
     }
 }
 
+// The same for bfloat16 rows whose widths are multiples of eight: a group of GS lanes (a power of two; dk / 8 of
+// them at work) holds a head, eight elements to a lane, so a warp takes 32 / GS heads at once with 16-byte
+// loads and stores.  The token's cosines and sines are made once, in shared memory, for all its heads; the
+// partner of a rotated element sits half / 8 lanes away (half a multiple of eight).  The arithmetic per
+// element is that of the kernel above.
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+template <int GS>
+__global__ void __launch_bounds__(256)
+qkv_unit_store_vec_kernel(const bf16* proj, int row_stride, const bf16* __restrict__ q_gain,
+                          const bf16* __restrict__ k_gain, float eps, int do_norm,
+                          const int* __restrict__ positions, const int* __restrict__ token_slot,
+                          const int* __restrict__ block_table, int max_pages, int page_size, bf16* k_plane,
+                          bf16* v_plane, long long page_stride, bf16* q_out, int q_heads, int kv_heads, int dk,
+                          int dv, int store, const float* __restrict__ inv_freq, int rot_dims, float temp_coef,
+                          int temp_every, int v_from_k) {
+    extern __shared__ float cos_sin[];                      // cos of the token's `half` angles, then their sines
+    TLLM_PDL_ENTER();
+    const int t = blockIdx.x;
+    const int slot = token_slot[t];
+    if (slot < 0) return;                                    // the whole block
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int pos = positions[t];
+    const int half = rot_dims >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * inv_freq[i];
+        cos_sin[i] = cosf(ang);
+        cos_sin[half + i] = sinf(ang);
+    }
+    if (half > 0) __syncthreads();
+    const bf16* row = proj + (size_t)t * row_stride;
+    long long page_base = -1;
+    int in_page = 0;
+    if (store) {
+        const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+        page_base = (long long)page * page_stride;
+        in_page = pos % page_size;
+        if (page < 0) store = 0;
+    }
+    constexpr int kPerWarp = 32 / GS;
+    const int grp = lane / GS, gl = lane % GS, e0 = gl * 8;
+    const int normed = q_heads + kv_heads;
+    const float q_temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
+    for (int base = warp * kPerWarp; base < normed; base += warps * kPerWarp) {
+        const int head = base + grp;
+        const bool is_q = head < q_heads;
+        const bool active = head < normed && e0 < dk;
+        float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        if (active) load8(row + (size_t)head * dk + e0, v);
+        float sum = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += v[e] * v[e];
+#pragma unroll
+        for (int o = GS / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float sc = do_norm ? 1.0f / sqrtf(sum / (float)dk + eps) : 1.0f;
+        const bf16* gain = is_q ? q_gain : k_gain;
+        if (active && gain != nullptr && do_norm) {
+            float gn[8];
+            load8(gain + e0, gn);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = v[e] * sc * gn[e];
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] *= sc;
+        }
+        if (half > 0) {                                      // every lane takes part in the exchange
+            const bool turns = e0 < rot_dims, low = e0 < half;
+            const int from = turns ? (low ? lane + half / 8 : lane - half / 8) : lane;
+            const int i0 = low ? e0 : e0 - half;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float y = __shfl_sync(0xffffffffu, v[e], from);
+                if (turns) {
+                    const float c = cos_sin[i0 + e], sn = cos_sin[half + i0 + e];
+                    v[e] = low ? v[e] * c - y * sn : v[e] * c + y * sn;
+                }
+            }
+        }
+        if (!active) continue;
+        bf16* dst;
+        if (is_q) dst = q_out + ((size_t)t * q_heads + head) * dk;
+        else if (store) dst = k_plane + page_base + ((size_t)(head - q_heads) * page_size + in_page) * dk;
+        else continue;
+        const float temp = is_q ? q_temp : 1.0f;
+        uint4 raw;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[2 * e] * temp, v[2 * e + 1] * temp);
+        *reinterpret_cast<uint4*>(dst + e0) = raw;
+    }
+    if (store) {
+        // values of their own, or the keys as they were projected (before their norm): 16 bytes a thread
+        const int per_head = dv / 8;
+        const bf16* src0 = v_from_k ? row + (size_t)q_heads * dk : row + (size_t)normed * dk;
+        for (int c = threadIdx.x; c < kv_heads * per_head; c += blockDim.x) {
+            const int g = c / per_head, j = c - g * per_head;
+            *reinterpret_cast<uint4*>(v_plane + page_base + ((size_t)g * page_size + in_page) * dv + j * 8) =
+                *reinterpret_cast<const uint4*>(src0 + (size_t)g * dv + j * 8);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- general kernel
 constexpr int kGenWarps = 4;
 
@@ -879,10 +990,28 @@ int tllm_qkv_unit_store(const void* proj, int row_stride, const void* q_gain, co
                row_stride, (const T*)q_gain, (const T*)k_gain, eps, do_norm, positions, token_slot,           \
                block_table, max_pages, page_size, (T*)k_plane, (T*)v_plane, page_stride, (T*)q_out, q_heads,  \
                kv_heads, dk, dv, store, inv_freq, rot_dims, temp_coef, temp_every, v_from_k)
-    if (dtype == kBF16) STORE(bf16);
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool vec = dtype == kBF16 && dk % 8 == 0 && dv % 8 == 0 && dk <= 256 && rot_dims % 16 == 0 &&
+                     row_stride % 8 == 0 && page_stride % 8 == 0 && aligned16(proj) && aligned16(q_out) &&
+                     aligned16(k_plane) && aligned16(v_plane) && aligned16(q_gain) && aligned16(k_gain);
+#define STORE_VEC(GS)                                                                                             \
+    launch_pdl(kPdlQk, qkv_unit_store_vec_kernel<GS>, dim3(tokens), dim3(256), (size_t)rot_dims * sizeof(float),  \
+               stream, (const bf16*)proj, row_stride, (const bf16*)q_gain, (const bf16*)k_gain, eps, do_norm,     \
+               positions, token_slot, block_table, max_pages, page_size, (bf16*)k_plane, (bf16*)v_plane,          \
+               page_stride, (bf16*)q_out, q_heads, kv_heads, dk, dv, store, inv_freq, rot_dims, temp_coef,        \
+               temp_every, v_from_k)
+    if (vec) {
+        if (dk <= 8) STORE_VEC(1);
+        else if (dk <= 16) STORE_VEC(2);
+        else if (dk <= 32) STORE_VEC(4);
+        else if (dk <= 64) STORE_VEC(8);
+        else if (dk <= 128) STORE_VEC(16);
+        else STORE_VEC(32);
+    } else if (dtype == kBF16) STORE(bf16);
     else if (dtype == kF32) STORE(float);
     else TLLM_REQUIRE(false, "qkv_unit_store: unknown dtype %d", dtype);
 #undef STORE
+#undef STORE_VEC
     return finish_launch("qkv_unit_store");
 }
 
