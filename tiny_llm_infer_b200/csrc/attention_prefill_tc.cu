@@ -490,6 +490,12 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
 #pragma unroll
                     for (int i = 0; i < kBN; ++i)
                         sv[i] = __float_as_uint(fmaf(__uint_as_float(sv[i]), scale_log2e, bias_far));
+                } else if (key0 + kBN - 1 <= t.first_pos && t.first_pos + kBM - 1 - key0 <= dist_len - 1) {
+                    // every distance of the tile lies inside the table: one pointer, constant offsets
+                    const float* at = bias_row + (pos - key0);
+#pragma unroll
+                    for (int i = 0; i < kBN; ++i)
+                        sv[i] = __float_as_uint(fmaf(__ldg(at - i), kLog2e, __uint_as_float(sv[i]) * scale_log2e));
                 } else {
                     const int d0 = pos - key0;                // the distance to key i of the tile is d0 - i
 #pragma unroll
