@@ -65,7 +65,7 @@ def test_config_errors():
             config_from_dict(bad)
 
 
-@pytest.mark.parametrize("rows,far", [(16, 120.0), (6, 9.0), (32, 256.0), (12, 50.0), (8, 64.0), (20, 1000.5)])
+@pytest.mark.parametrize("rows,far", [(16, 100.0), (6, 9.0), (32, 256.0), (12, 50.0), (8, 64.0), (20, 1000.5)])
 def test_distance_buckets(rows, far):
     table = distance_buckets(rows, far)
     for n in range(3 * int(far)):

@@ -221,7 +221,7 @@ def tie_keys_to_queries(H, G, dk, hidden):
 
 KEYED_CASES = [dict(H=4, G=2, dk=32, scale=0.3, far=50.0, coef=0.4, every=16, rows=12, page=16),
                dict(H=1, G=1, dk=20, scale=0.35, far=9.0, coef=1.0, every=3, rows=6, page=8),
-               dict(H=8, G=2, dk=64, scale=0.125, far=200.0, coef=0.3, every=50, rows=16, page=32),
+               dict(H=8, G=2, dk=64, scale=0.125, far=200.0, coef=0.35, every=50, rows=16, page=32),
                dict(H=6, G=6, dk=128, scale=0.09, far=64.0, coef=0.5, every=100, rows=8, page=16),
                dict(H=3, G=1, dk=44, scale=0.2, far=1000.5, coef=0.0, every=1, rows=20, page=16)]
 
@@ -256,7 +256,7 @@ def test_attention_with_keys_as_values(case, dtype):
 
 ROTARY_CASES = [dict(H=6, G=3, dk=40, dv=24, scale=0.25, base=10000.0, dims=16, page=16),
                 dict(H=3, G=1, dk=10, dv=6, scale=0.4, base=77.0, dims=4, page=8),
-                dict(H=4, G=2, dk=128, dv=128, scale=0.09, base=500000.0, dims=64, page=32),
+                dict(H=4, G=2, dk=128, dv=128, scale=0.09, base=400000.0, dims=64, page=32),
                 dict(H=5, G=5, dk=12, dv=20, scale=0.3, base=250000.0, dims=12, page=16),
                 dict(H=8, G=2, dk=80, dv=176, scale=0.1, base=1e6, dims=80, page=16),
                 dict(H=2, G=2, dk=64, dv=64, scale=0.125, base=300.0, dims=2, page=16)]
@@ -361,7 +361,7 @@ def recurrence_run(part, w64, plain_fn, dtype, hidden, lengths=(230, 61, 1), see
     return whole_then_portions(Bench(part, dtype, xs, want), lengths)
 
 
-MEMORY_CASES = [dict(H=2, dk=24, dv=40, cap=8.0), dict(H=1, dk=10, dv=6, cap=3.0, reach=40), dict(H=2, dk=128, dv=64, cap=15.0),
+MEMORY_CASES = [dict(H=2, dk=24, dv=40, cap=8.0), dict(H=1, dk=10, dv=6, cap=3.0, reach=40), dict(H=2, dk=128, dv=64, cap=14.0),
                 dict(H=3, dk=40, dv=72, cap=6.0), dict(H=4, dk=16, dv=16, cap=20.0), dict(H=5, dk=7, dv=2, cap=1.5, reach=20)]
 
 

@@ -42,7 +42,7 @@ T1 = dict(cfg=TetodraConfig(vocab=320, width=128, embedding_scale=6.0, norm_eps=
     keyed(4, 2, 32, 0.3, 50.0, 0.4, 16, 12, (2, 24, 40, 8.0), ff=160),
     delta(4, 2, 16, 24, 4),
     rotary(6, 3, 40, 24, 0.25, 10000.0, 16, (3, 24, 32, 4.0, 16), ff=96),
-    keyed(2, 2, 48, 0.2, 120.0, 0.2, 64, 20, (4, 16, 16, 20.0)),
+    keyed(2, 2, 48, 0.2, 110.0, 0.2, 64, 20, (4, 16, 16, 20.0)),
 )), seed=41, std=0.08, norm_range=(0.7, 1.3), page_size=16, lengths=(70, 97, 130, 41, 66, 35))
 # nothing a multiple of eight, little a multiple of four; one head alone; pages of 8; a table of 6 rows reaching 9
 T2 = dict(cfg=TetodraConfig(vocab=401, width=100, embedding_scale=1.0, norm_eps=3e-6, residual_mult=1.0, layers=(
@@ -54,9 +54,9 @@ T2 = dict(cfg=TetodraConfig(vocab=401, width=100, embedding_scale=1.0, norm_eps=
 )), seed=42, std=0.12, norm_range=(0.6, 1.4), page_size=8, lengths=(70, 97, 41, 35, 66))
 # keys and values of 64 and 128 (the tensor-core kernels' own widths), pages of 32, prompts of hundreds of tokens;
 # a table reaching 200 tokens and a temperature that steps every 50
-T3 = dict(cfg=TetodraConfig(vocab=512, width=192, embedding_scale=12.0, norm_eps=1e-6, residual_mult=0.8, layers=(
-    rotary(4, 2, 128, 128, 0.09, 500000.0, 64, (2, 64, 64, 16.0, 24), ff=256),
-    keyed(8, 2, 64, 0.125, 200.0, 0.3, 50, 16, (2, 128, 64, 15.0), ff=256),
+T3 = dict(cfg=TetodraConfig(vocab=512, width=224, embedding_scale=12.0, norm_eps=1e-6, residual_mult=0.8, layers=(
+    rotary(4, 2, 128, 128, 0.09, 400000.0, 64, (2, 64, 64, 12.0, 24), ff=256),
+    keyed(8, 2, 64, 0.125, 200.0, 0.35, 50, 16, (2, 128, 64, 14.0), ff=256),
     delta(2, 1, 128, 128, 3, ff=128),
     keyed(2, 1, 128, 0.09, 64.0, 0.5, 100, 8, (3, 40, 72, 6.0)),
 )), seed=43, std=0.07, norm_range=(0.8, 1.2), page_size=32, lengths=(70, 300, 130, 41, 210, 35))
