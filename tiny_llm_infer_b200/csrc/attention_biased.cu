@@ -32,7 +32,13 @@ struct ScoreMod {
     int chunk, window, sink;
     const float* dist_bias;      // [query heads][dist_len] float32 added to the score by distance, or null
     int dist_len;                // distances from dist_len - 1 on share the last entry
+    int gate_per_head;           // the output gate holds one number per query head instead of one per element
 };
+
+// Place of the gate of element e of a head within the token's gate row.
+__device__ __forceinline__ size_t gate_at(int per_head, int head, int dv, int e) {
+    return per_head ? (size_t)head : (size_t)head * dv + e;
+}
 
 // The learned bias of a head for a key `dist` tokens back (0 without a table).
 __device__ __forceinline__ float dist_bias_of(const ScoreMod& m, int head, int dist) {
@@ -69,7 +75,7 @@ __global__ void qkv_unit_store_kernel(const T* proj, int row_stride, const T* __
                                       T* k_plane, T* v_plane, long long page_stride, T* q_out,
                                       int q_heads, int kv_heads, int dk, int dv, int store,
                                       const float* __restrict__ inv_freq, int rot_dims, float temp_coef,
-                                      int temp_every, int v_from_k) {
+                                      int temp_every, int v_from_k, const float* __restrict__ bias) {
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const int slot = token_slot[t];
@@ -77,6 +83,8 @@ __global__ void qkv_unit_store_kernel(const T* proj, int row_stride, const T* __
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int pos = positions[t];
     const T* row = proj + (size_t)t * row_stride;
+    // element c of the row as the kernel sees it: the projection plus its bias, if it has one, in float32
+    auto at = [&](size_t c) -> float { return to_f32<T>(row[c]) + (bias != nullptr ? bias[c] : 0.0f); };
     long long page_base = -1;
     int in_page = 0;
     if (store) {
@@ -89,11 +97,11 @@ __global__ void qkv_unit_store_kernel(const T* proj, int row_stride, const T* __
     for (int head = warp; head < total; head += warps) {
         if (head < q_heads + kv_heads) {
             const bool is_q = head < q_heads;
-            const T* src = row + (size_t)head * dk;
+            const size_t src = (size_t)head * dk;
             const T* gain = is_q ? q_gain : k_gain;
             float sum = 0.0f;
             for (int e = lane; e < dk; e += 32) {
-                const float x = to_f32<T>(src[e]);
+                const float x = at(src + e);
                 sum += x * x;
             }
             sum = warp_sum(sum);
@@ -106,11 +114,11 @@ __global__ void qkv_unit_store_kernel(const T* proj, int row_stride, const T* __
             const float temp = (is_q && temp_every > 0) ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
             const int half = rot_dims >> 1;
             for (int e = lane; e < dk; e += 32) {
-                float x = to_f32<T>(src[e]) * sc;
+                float x = at(src + e) * sc;
                 if (gain != nullptr && do_norm) x *= to_f32<T>(gain[e]);
                 if (e < rot_dims) {               // element e turns with its partner half a rotated width away
                     const int partner = e < half ? e + half : e - half;
-                    float y = to_f32<T>(src[partner]) * sc;
+                    float y = at(src + partner) * sc;
                     if (gain != nullptr && do_norm) y *= to_f32<T>(gain[partner]);
                     const float ang = (float)pos * inv_freq[e < half ? e : e - half];
                     const float c = cosf(ang), sn = sinf(ang);
@@ -121,10 +129,11 @@ __global__ void qkv_unit_store_kernel(const T* proj, int row_stride, const T* __
         } else if (store) {
             const int g = head - q_heads - kv_heads;
             // values of their own, or the keys as they were projected (before their norm)
-            const T* src = v_from_k ? row + (size_t)(q_heads + g) * dk
-                                    : row + (size_t)(q_heads + kv_heads) * dk + (size_t)g * dv;
+            const size_t src = v_from_k ? (size_t)(q_heads + g) * dk
+                                        : (size_t)(q_heads + kv_heads) * dk + (size_t)g * dv;
             T* dst = v_plane + page_base + ((size_t)g * page_size + in_page) * dv;
-            for (int e = lane; e < dv; e += 32) dst[e] = src[e];
+            if (bias != nullptr) for (int e = lane; e < dv; e += 32) dst[e] = from_f32<T>(at(src + e));
+            else for (int e = lane; e < dv; e += 32) dst[e] = row[src + e];
         }
     }
 }
@@ -153,7 +162,7 @@ qkv_unit_store_vec_kernel(const bf16* proj, int row_stride, const bf16* __restri
                           const int* __restrict__ block_table, int max_pages, int page_size, bf16* k_plane,
                           bf16* v_plane, long long page_stride, bf16* q_out, int q_heads, int kv_heads, int dk,
                           int dv, int store, const float* __restrict__ inv_freq, int rot_dims, float temp_coef,
-                          int temp_every, int v_from_k) {
+                          int temp_every, int v_from_k, const float* __restrict__ bias) {
     extern __shared__ float cos_sin[];                      // cos of the token's `half` angles, then their sines
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
@@ -186,7 +195,15 @@ qkv_unit_store_vec_kernel(const bf16* proj, int row_stride, const bf16* __restri
         const bool is_q = head < q_heads;
         const bool active = head < normed && e0 < dk;
         float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-        if (active) load8(row + (size_t)head * dk + e0, v);
+        if (active) {
+            load8(row + (size_t)head * dk + e0, v);
+            if (bias != nullptr) {                           // the projection's bias, added in float32
+                const float4 b0 = *reinterpret_cast<const float4*>(bias + (size_t)head * dk + e0);
+                const float4 b1 = *reinterpret_cast<const float4*>(bias + (size_t)head * dk + e0 + 4);
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+            }
+        }
         float sum = 0.0f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) sum += v[e] * v[e];
@@ -234,8 +251,19 @@ qkv_unit_store_vec_kernel(const bf16* proj, int row_stride, const bf16* __restri
         const bf16* src0 = v_from_k ? row + (size_t)q_heads * dk : row + (size_t)normed * dk;
         for (int c = threadIdx.x; c < kv_heads * per_head; c += blockDim.x) {
             const int g = c / per_head, j = c - g * per_head;
-            *reinterpret_cast<uint4*>(v_plane + page_base + ((size_t)g * page_size + in_page) * dv + j * 8) =
-                *reinterpret_cast<const uint4*>(src0 + (size_t)g * dv + j * 8);
+            bf16* dst = v_plane + page_base + ((size_t)g * page_size + in_page) * dv + j * 8;
+            if (bias == nullptr) {
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src0 + (size_t)g * dv + j * 8);
+                continue;
+            }
+            float v[8];
+            load8(src0 + (size_t)g * dv + j * 8, v);
+            const float* b = bias + (src0 - row) + (size_t)g * dv + j * 8;
+            uint4 raw;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[2 * e] + b[2 * e], v[2 * e + 1] + b[2 * e + 1]);
+            *reinterpret_cast<uint4*>(dst) = raw;
         }
     }
 }
@@ -323,13 +351,13 @@ __global__ void attention_biased_general_kernel(
         total += l_s[w] * w_scale[w];
     }
     const float inv = total > 0.0f ? 1.0f / total : 0.0f;
-    const T* grow = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)head * dv : nullptr;
+    const T* grow = gate != nullptr ? gate + (size_t)t * gate_stride + gate_at(mod.gate_per_head, head, dv, 0) : nullptr;
     for (int e = threadIdx.x; e < dv; e += blockDim.x) {
         float v = 0.0f;
 #pragma unroll
         for (int w = 0; w < kGenWarps; ++w) v += acc_s[w * dv + e] * w_scale[w];
         v *= inv;
-        if (grow != nullptr) v *= 1.0f / (1.0f + expf(-to_f32<T>(grow[e])));
+        if (grow != nullptr) v *= 1.0f / (1.0f + expf(-to_f32<T>(grow[mod.gate_per_head ? 0 : e])));
         dst[e] = from_f32<T>(v);
     }
 }
@@ -618,8 +646,9 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
     const size_t row_lo = start + q_off + r_lo, row_hi = start + q_off + r_hi;
     bf16* o_lo = out + (row_lo * q_heads + head) * dv;
     bf16* o_hi = out + (row_hi * q_heads + head) * dv;
-    const bf16* g_lo = gate != nullptr ? gate + row_lo * gate_stride + (size_t)head * dv : nullptr;
-    const bf16* g_hi = gate != nullptr ? gate + row_hi * gate_stride + (size_t)head * dv : nullptr;
+    const bf16* g_lo = gate != nullptr ? gate + row_lo * gate_stride + gate_at(mod.gate_per_head, head, dv, 0) : nullptr;
+    const bf16* g_hi = gate != nullptr ? gate + row_hi * gate_stride + gate_at(mod.gate_per_head, head, dv, 0) : nullptr;
+    const int g_step = mod.gate_per_head ? 0 : 1;
 #pragma unroll
     for (int i = 0; i < DVP / 8; ++i) {
         const int col = i * 8 + (lane & 3) * 2;
@@ -627,16 +656,16 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
         if (v_lo) {
             float a = o[i][0] * inv_lo, b = o[i][1] * inv_lo;
             if (g_lo != nullptr) {
-                a *= 1.0f / (1.0f + expf(-__bfloat162float(g_lo[col])));
-                b *= 1.0f / (1.0f + expf(-__bfloat162float(g_lo[col + 1])));
+                a *= 1.0f / (1.0f + expf(-__bfloat162float(g_lo[col * g_step])));
+                b *= 1.0f / (1.0f + expf(-__bfloat162float(g_lo[(col + 1) * g_step])));
             }
             *reinterpret_cast<uint32_t*>(o_lo + col) = pack_bf16(a, b);
         }
         if (v_hi) {
             float a = o[i][2] * inv_hi, b = o[i][3] * inv_hi;
             if (g_hi != nullptr) {
-                a *= 1.0f / (1.0f + expf(-__bfloat162float(g_hi[col])));
-                b *= 1.0f / (1.0f + expf(-__bfloat162float(g_hi[col + 1])));
+                a *= 1.0f / (1.0f + expf(-__bfloat162float(g_hi[col * g_step])));
+                b *= 1.0f / (1.0f + expf(-__bfloat162float(g_hi[(col + 1) * g_step])));
             }
             *reinterpret_cast<uint32_t*>(o_hi + col) = pack_bf16(a, b);
         }
@@ -893,7 +922,7 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
         }
         v = total > 0.0f ? v / total : 0.0f;
         if (gate != nullptr)
-            v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + (size_t)(head0 + h) * dv + e])));
+            v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + gate_at(mod.gate_per_head, head0 + h, dv, e)])));
         out[((size_t)t * q_heads + head0 + h) * dv + e] = __float2bfloat16_rn(v);
     }
 }
@@ -901,7 +930,8 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
 // The runs of a (row, head) added in their order, the gate applied, the result written.
 __global__ void attention_biased_combine_kernel(const float* part, const int* __restrict__ token_slot,
                                                 const int* __restrict__ rows, int q_heads, int dv, int splits,
-                                                const bf16* gate, int gate_stride, bf16* __restrict__ out) {
+                                                const bf16* gate, int gate_stride, int gate_per_head,
+                                                bf16* __restrict__ out) {
     TLLM_PDL_ENTER();
     const int t = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
     const int head = blockIdx.y, rec = dv + 2;
@@ -922,7 +952,7 @@ __global__ void attention_biased_combine_kernel(const float* part, const int* __
             v += src[s2 * rec + e] * w;
         }
         v = total > 0.0f ? v / total : 0.0f;
-        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + (size_t)head * dv + e])));
+        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + gate_at(gate_per_head, head, dv, e)])));
         dst[e] = __float2bfloat16_rn(v);
     }
 }
@@ -956,7 +986,7 @@ static int launch_biased_decode(const void* q, const void* kp, const void* vp, l
                (const bf16*)gate, gate_stride, splits, sub_groups, part, (bf16*)out);
     if (splits > 1)
         launch_pdl(kPdlCombine, attention_biased_combine_kernel, dim3(n_rows, q_heads), dim3(dv >= 128 ? 128 : 64), 0, stream,
-                   (const float*)part, token_slot, rows, q_heads, dv, splits, (const bf16*)gate, gate_stride, (bf16*)out);
+                   (const float*)part, token_slot, rows, q_heads, dv, splits, (const bf16*)gate, gate_stride, mod.gate_per_head, (bf16*)out);
     return finish_launch("attention_biased_decode");
 }
 
@@ -971,7 +1001,7 @@ int tllm_qkv_unit_store(const void* proj, int row_stride, const void* q_gain, co
                         int max_pages, int page_size, void* k_plane, void* v_plane, long long page_stride,
                         void* q_out, int dtype, int tokens, int q_heads, int kv_heads, int dk, int dv,
                         int store, const float* inv_freq, int rot_dims, float temp_coef, int temp_every, int v_from_k,
-                        cudaStream_t stream) {
+                        const float* bias, cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && dk > 0 && dv > 0, "qkv_unit_store: bad sizes");
     TLLM_REQUIRE(row_stride >= (q_heads + kv_heads) * dk + (v_from_k ? 0 : kv_heads * dv), "qkv_unit_store: rows of %d are too short", row_stride);
     TLLM_REQUIRE(rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq != nullptr),
@@ -989,17 +1019,17 @@ int tllm_qkv_unit_store(const void* proj, int row_stride, const void* q_gain, co
     launch_pdl(kPdlQk, qkv_unit_store_kernel<T>, dim3(tokens), dim3(warps * 32), 0, stream, (const T*)proj,   \
                row_stride, (const T*)q_gain, (const T*)k_gain, eps, do_norm, positions, token_slot,           \
                block_table, max_pages, page_size, (T*)k_plane, (T*)v_plane, page_stride, (T*)q_out, q_heads,  \
-               kv_heads, dk, dv, store, inv_freq, rot_dims, temp_coef, temp_every, v_from_k)
+               kv_heads, dk, dv, store, inv_freq, rot_dims, temp_coef, temp_every, v_from_k, bias)
     auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool vec = dtype == kBF16 && dk % 8 == 0 && dv % 8 == 0 && dk <= 256 && rot_dims % 16 == 0 &&
                      row_stride % 8 == 0 && page_stride % 8 == 0 && aligned16(proj) && aligned16(q_out) &&
-                     aligned16(k_plane) && aligned16(v_plane) && aligned16(q_gain) && aligned16(k_gain);
+                     aligned16(k_plane) && aligned16(v_plane) && aligned16(q_gain) && aligned16(k_gain) && aligned16(bias);
 #define STORE_VEC(GS)                                                                                             \
     launch_pdl(kPdlQk, qkv_unit_store_vec_kernel<GS>, dim3(tokens), dim3(256), (size_t)rot_dims * sizeof(float),  \
                stream, (const bf16*)proj, row_stride, (const bf16*)q_gain, (const bf16*)k_gain, eps, do_norm,     \
                positions, token_slot, block_table, max_pages, page_size, (bf16*)k_plane, (bf16*)v_plane,          \
                page_stride, (bf16*)q_out, q_heads, kv_heads, dk, dv, store, inv_freq, rot_dims, temp_coef,        \
-               temp_every, v_from_k)
+               temp_every, v_from_k, bias)
     if (vec) {
         if (dk <= 8) STORE_VEC(1);
         else if (dk <= 16) STORE_VEC(2);
@@ -1019,7 +1049,7 @@ int tllm_attention_biased_general(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* positions,
     const int* token_slot, const int* block_table, int max_pages, int page_size, int dtype, int tokens,
     int q_heads, int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const float* sink_logit, const float* dist_bias, int dist_len, int v_row, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    const float* slopes, const float* sink_logit, const float* dist_bias, int dist_len, int v_row, const void* gate, int gate_stride, int gate_per_head, void* out, cudaStream_t stream) {
     if (v_row <= 0) v_row = dv;
     TLLM_REQUIRE(dist_bias == nullptr || dist_len > 0, "attention_biased: an empty table of biases");
     TLLM_REQUIRE(v_row >= dv, "attention_biased: values of width %d in rows of %d", dv, v_row);
@@ -1030,7 +1060,7 @@ int tllm_attention_biased_general(
     TLLM_REQUIRE(tokens <= 65535, "attention_biased: %d tokens in one step exceed 65535", tokens);
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased: negative constant");
     if (tokens == 0) return 0;
-    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len};
+    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len, gate_per_head ? 1 : 0};
     if (dtype == kBF16)
         return launch_general<bf16>(q, k_plane, v_plane, page_stride, positions, token_slot, block_table, max_pages,
                                     page_size, tokens, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, out, stream);
@@ -1053,16 +1083,16 @@ int tllm_attention_biased_prefill(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* seg_info,
     const int* tiles, int n_tiles, const int* block_table, int max_pages, int page_size, int q_heads,
     int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const float* sink_logit, const float* dist_bias, int dist_len, int v_row, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    const float* slopes, const float* sink_logit, const float* dist_bias, int dist_len, int v_row, const void* gate, int gate_stride, int gate_per_head, void* out, cudaStream_t stream) {
     if (v_row <= 0) v_row = dv;
     TLLM_REQUIRE(dist_bias == nullptr || dist_len > 0, "attention_biased_prefill: an empty table of biases");
     TLLM_REQUIRE(v_row >= dv && v_row % 8 == 0, "attention_biased_prefill: values of width %d in rows of %d", dv, v_row);
     TLLM_REQUIRE(tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv), "attention_biased_prefill: sizes %d/%d heads, widths %d/%d", q_heads, kv_heads, dk, dv);
     TLLM_REQUIRE(page_size > 0 && max_pages > 0 && n_tiles >= 0 && q_heads <= 65535, "attention_biased_prefill: bad geometry");
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_prefill: negative constant");
-    TLLM_REQUIRE(gate == nullptr || gate_stride % 2 == 0, "attention_biased_prefill: odd gate stride");
+    TLLM_REQUIRE(gate == nullptr || gate_per_head || gate_stride % 2 == 0, "attention_biased_prefill: odd gate stride");
     if (n_tiles == 0) return 0;
-    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len};
+    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len, gate_per_head ? 1 : 0};
 #define PF(A, B) launch_biased_prefill<A, B>(q, k_plane, v_plane, page_stride, seg_info, tiles, n_tiles, block_table, max_pages, \
                                              page_size, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, out, stream)
     if (dk <= 64) return dv <= 64 ? PF(64, 64) : PF(64, 128);
@@ -1077,7 +1107,7 @@ int tllm_attention_biased_decode(
     const int* token_slot, const int* rows, int n_rows, const int* block_table, int max_pages, int page_size,
     int q_heads, int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
     const float* slopes, const float* sink_logit, const float* dist_bias, int dist_len, int v_row, const void* gate,
-    int gate_stride, int splits, float* part, void* out, cudaStream_t stream) {
+    int gate_stride, int gate_per_head, int splits, float* part, void* out, cudaStream_t stream) {
     if (v_row <= 0) v_row = dv;
     TLLM_REQUIRE(dist_bias == nullptr || dist_len > 0, "attention_biased_decode: an empty table of biases");
     TLLM_REQUIRE(v_row >= dv && v_row % 8 == 0, "attention_biased_decode: values of width %d in rows of %d", dv, v_row);
@@ -1086,7 +1116,7 @@ int tllm_attention_biased_decode(
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_decode: negative constant");
     TLLM_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || part != nullptr), "attention_biased_decode: %d runs of keys", splits);
     if (n_rows == 0) return 0;
-    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len};
+    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0, dist_bias, dist_len, gate_per_head ? 1 : 0};
 #define DEC(A, B) launch_biased_decode<A, B>(q, k_plane, v_plane, page_stride, positions, token_slot, rows, n_rows, block_table, \
                                              max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, \
                                              splits, part, out, stream)

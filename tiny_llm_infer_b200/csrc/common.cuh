@@ -23,13 +23,17 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
 // Activation of the gate in a gated feed-forward unit, act(gate) * up, by code.
-enum GateAct : int { kActSilu = 0, kActGeluTanh = 1, kActGeluErf = 2 };
+enum GateAct : int { kActSilu = 0, kActGeluTanh = 1, kActGeluErf = 2, kActRelu2 = 3 };
 
 __device__ __forceinline__ float gate_act(float g, int act) {
     if (act == kActGeluTanh)   // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
         return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     if (act == kActGeluErf)    // 0.5 g (1 + erf(g / sqrt(2)))
         return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
+    if (act == kActRelu2) {    // max(g, 0)^2
+        const float r = fmaxf(g, 0.0f);
+        return r * r;
+    }
     return g / (1.0f + expf(-g));
 }
 

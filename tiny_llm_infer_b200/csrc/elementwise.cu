@@ -204,6 +204,95 @@ __global__ void add_rmsnorm_vec_kernel(float* h, const TD* delta,
     }
 }
 
+// ---------------------------------------------------------------- norm of a weighted sum, written back as the stream
+// For layers that norm after the sum:  v = alpha * h[r, :] + sum_i c_i * d_i[r, :] (+ bias[:]);
+// h[r, :] = gain * v / sqrt(mean(v^2) + eps)  (float32, the new stream), out[r, :] = the same in the storage
+// type, which the next sub-layer reads.  Up to kMaxSumTerms outputs d_i in the storage type, each with one
+// float32 number c_i; gain and bias are float32 vectors.  With no outputs and alpha = 1 it is the plain norm
+// of the stream.
+constexpr int kMaxSumTerms = 4;
+struct SumTerms {
+    const void* d[kMaxSumTerms];
+    float c[kMaxSumTerms];
+    int n;
+};
+
+template <typename TD>
+__global__ void sum_rmsnorm_kernel(float* h, SumTerms ts, float alpha, const float* __restrict__ bias,
+                                   const float* __restrict__ gain, float eps, TD* __restrict__ out, int width) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int r = blockIdx.x;
+    float* hr = h + (size_t)r * width;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = alpha * hr[i];
+        for (int k = 0; k < ts.n; ++k) v += ts.c[k] * to_f32<TD>(((const TD*)ts.d[k])[(size_t)r * width + i]);
+        if (bias != nullptr) v += bias[i];
+        hr[i] = v;
+        sum += v * v;
+    }
+    sum = block_sum(sum, scratch);
+    const float scale = 1.0f / sqrtf(sum / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = gain[i] * hr[i] * scale;
+        hr[i] = v;
+        out[(size_t)r * width + i] = from_f32<TD>(v);
+    }
+}
+
+template <typename TD, int CHUNKS, int N>
+__global__ void sum_rmsnorm_vec_kernel(float* h, SumTerms ts, float alpha, const float* __restrict__ bias,
+                                       const float* __restrict__ gain, float eps, TD* __restrict__ out, int width) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int r = blockIdx.x;
+    const int n_chunks = width >> 3;
+    float* hr = h + (size_t)r * width;
+    float v[CHUNKS][8], d[CHUNKS][N > 0 ? N : 1][8];
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            Vec8<float>::load(hr + c * 8, v[j]);
+#pragma unroll
+            for (int k = 0; k < N; ++k) Vec8<TD>::load((const TD*)ts.d[k] + (size_t)r * width + c * 8, d[j][k]);
+        }
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (bias != nullptr) Vec8<float>::load(bias + c * 8, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float x = alpha * v[j][e];
+#pragma unroll
+                for (int k = 0; k < N; ++k) x += ts.c[k] * d[j][k][e];
+                x += b[e];
+                v[j][e] = x;
+                sum += x * x;
+            }
+        }
+    }
+    sum = block_sum(sum, scratch);
+    const float scale = 1.0f / sqrtf(sum / (float)width + eps);
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            float g[8];
+            Vec8<float>::load(gain + c * 8, g);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] = g[e] * v[j][e] * scale;
+            Vec8<float>::store(hr + c * 8, g);
+            Vec8<TD>::store(out + (size_t)r * width + c * 8, g);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- scaled sum of several outputs + layer norm
 // For blocks whose sub-layers all read one norm's output and whose outputs are added together, each times a
 // vector of its own (a layer scale, a mixing weight, a residual multiplier, all folded into one float32 vector
@@ -808,11 +897,60 @@ static int launch_scaled_layernorm_typed(float* h, const ScaledDeltas& ds, const
     return finish_launch("scaled_add_layernorm");
 }
 
+template <typename TD>
+static int launch_sum_rmsnorm_typed(float* h, const SumTerms& ts, float alpha, const float* bias, const float* gain,
+                                    float eps, void* out, int n_rows, int width, cudaStream_t stream) {
+    bool vec = width % 8 == 0 && aligned16(h) && aligned16(gain) && aligned16(out) && aligned16(bias);
+    for (int k = 0; k < ts.n; ++k) vec = vec && aligned16(ts.d[k]);
+    const int chunks = width / 8;
+    if (vec && chunks <= 1024 * 4) {
+        int block = 64;
+        while (block < 1024 && block < chunks) block *= 2;
+        const int per_thread = (chunks + block - 1) / block;
+#define VEC_LAUNCH_N(C, N)                                                                                 \
+    launch_pdl(kPdlNorm, sum_rmsnorm_vec_kernel<TD, C, N>, dim3(n_rows), dim3(block), 0, stream, h, ts,    \
+               alpha, bias, gain, eps, (TD*)out, width)
+#define VEC_LAUNCH(C)                                            \
+    switch (ts.n) {                                              \
+        case 0: VEC_LAUNCH_N(C, 0); break;                       \
+        case 1: VEC_LAUNCH_N(C, 1); break;                       \
+        case 2: VEC_LAUNCH_N(C, 2); break;                       \
+        case 3: VEC_LAUNCH_N(C, 3); break;                       \
+        default: VEC_LAUNCH_N(C, 4); break;                      \
+    }
+        if (per_thread <= 1) { VEC_LAUNCH(1) }
+        else if (per_thread <= 2) { VEC_LAUNCH(2) }
+        else { VEC_LAUNCH(4) }
+#undef VEC_LAUNCH
+#undef VEC_LAUNCH_N
+    } else {
+        const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+        launch_pdl(kPdlNorm, sum_rmsnorm_kernel<TD>, dim3(n_rows), dim3(block), 0, stream, h, ts, alpha, bias, gain,
+                   eps, (TD*)out, width);
+    }
+    return finish_launch("sum_rmsnorm");
+}
+
 }  // namespace tllm
 
 using namespace tllm;
 
 extern "C" {
+
+// h <- gain * v / sqrt(mean(v^2) + eps) with v = alpha * h + sum_i coefs[i] * deltas[i] (+ bias), every row; out gets
+// the new h in the storage type `act_dtype` (that of the deltas).  gain and bias float32; bias may be null.
+int tllm_sum_rmsnorm(float* h, const void* const* deltas, const float* coefs, int n, float alpha, const float* bias,
+                     const float* gain, float eps, void* out, int act_dtype, int n_rows, int width, cudaStream_t stream) {
+    TLLM_REQUIRE(n_rows >= 0 && width > 0 && n >= 0 && n <= kMaxSumTerms, "sum_rmsnorm: bad sizes");
+    TLLM_REQUIRE(eps > 0.0f && gain != nullptr && out != nullptr, "sum_rmsnorm: missing operand");
+    if (n_rows == 0) return 0;
+    SumTerms ts;
+    ts.n = n;
+    for (int k = 0; k < kMaxSumTerms; ++k) { ts.d[k] = k < n ? deltas[k] : nullptr; ts.c[k] = k < n ? coefs[k] : 0.0f; }
+    if (act_dtype == kBF16) return launch_sum_rmsnorm_typed<bf16>(h, ts, alpha, bias, gain, eps, out, n_rows, width, stream);
+    if (act_dtype == kF32) return launch_sum_rmsnorm_typed<float>(h, ts, alpha, bias, gain, eps, out, n_rows, width, stream);
+    TLLM_REQUIRE(false, "sum_rmsnorm: unknown dtype %d", act_dtype);
+}
 
 // h += sum over `n` outputs of scales[i] * deltas[i] (float32 vectors of the row's width; outputs in the
 // storage type), then the layer norm of the sum (mean taken off, gain, no bias).  `n` may be 0.
@@ -932,7 +1070,7 @@ int tllm_softcap(float* x, float cap, long long n, cudaStream_t stream) {
 // out = act(x), times table[ids[t], col0 + j] where a table is given (x and out [tokens, width]).
 int tllm_activation(const void* x, void* out, int dtype, int act, int tokens, int width, const int* ids,
                     const void* table, int ldt, int col0, int vocab, cudaStream_t stream) {
-    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh || act == kActGeluErf, "activation: unknown activation %d", act);
+    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh || act == kActGeluErf || act == kActRelu2, "activation: unknown activation %d", act);
     TLLM_REQUIRE(tokens >= 0 && width > 0, "activation: bad sizes");
     TLLM_REQUIRE(table == nullptr || (ids != nullptr && col0 >= 0 && col0 + width <= ldt && vocab > 0), "activation: bad table");
     const size_t total = (size_t)tokens * width;

@@ -254,7 +254,7 @@ extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, in
 // exact GELU on every output, in the same kernel.
 extern "C" int tllm_gemm_skinny_act(const void* x, const void* w, void* y, int M, int N, int K, int act,
                                     cudaStream_t stream) {
-    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh || act == kActGeluErf, "gemm_skinny_act: unknown activation %d", act);
+    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh || act == kActGeluErf || act == kActRelu2, "gemm_skinny_act: unknown activation %d", act);
     TLLM_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny_act: bad sizes");
     TLLM_REQUIRE(M <= 8, "gemm_skinny_act: %d rows exceed 8", M);
     TLLM_REQUIRE(K % 8 == 0, "gemm_skinny_act: K = %d is no multiple of 8", K);
@@ -262,6 +262,7 @@ extern "C" int tllm_gemm_skinny_act(const void* x, const void* w, void* y, int M
                  "gemm_skinny_act: operands must be 16-byte aligned");
     if (M == 0) return 0;
     if (act == kActGeluErf) return launch_skinny<1, bf16, false, 3, kActGeluErf, true>(x, w, y, M, N, K, stream);
+    if (act == kActRelu2) return launch_skinny<1, bf16, false, 3, kActRelu2, true>(x, w, y, M, N, K, stream);
     if (act == kActGeluTanh) return launch_skinny<1, bf16, false, 3, kActGeluTanh, true>(x, w, y, M, N, K, stream);
     return launch_skinny<1, bf16, false, 3, kActSilu, true>(x, w, y, M, N, K, stream);
 }

@@ -56,6 +56,7 @@ template <int ACT>
 __device__ __forceinline__ float unary_act(float g) {
     if (ACT == kActGeluErf) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
     if (ACT == kActNone) return g;
+    if (ACT == kActRelu2) { const float r = fmaxf(g, 0.0f); return r * r; }
     return fast_gate_act<ACT>(g);
 }
 
@@ -511,6 +512,7 @@ extern "C" int tllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, i
         if (act == kActGeluErf) return UNARY(kActGeluErf);
         if (act == kActGeluTanh) return UNARY(kActGeluTanh);
         if (act == kActSilu) return UNARY(kActSilu);
+        if (act == kActRelu2) return UNARY(kActRelu2);
 #undef UNARY
         TLLM_REQUIRE(false, "gemm_tcgen05: unknown activation %d", act);
     }
@@ -544,6 +546,16 @@ extern "C" int tllm_gemm_tcgen05_grouped(const void* x, const void* w, void* y, 
                  "gemm_tcgen05_grouped: cuTensorMapEncodeTiled failed or is not available");
     const GroupedTiles grouped{tile_expert, tile_row0, n_tiles, offsets, n};
     const int act = flags >> 8;
+    if (flags & 16) {                                       // a plain product with an activation on every output
+        TLLM_REQUIRE(!gated, "gemm_tcgen05_grouped: either a gated or a plain activation");
+#define UNARY(A) launch_tcgen05<false, 1, A>(mx, mw, y, rows, n, K, 0, 0, error_word, stream, grouped, max_tiles)
+        if (act == kActRelu2) return UNARY(kActRelu2);
+        if (act == kActSilu) return UNARY(kActSilu);
+        if (act == kActGeluTanh) return UNARY(kActGeluTanh);
+        if (act == kActGeluErf) return UNARY(kActGeluErf);
+#undef UNARY
+        TLLM_REQUIRE(false, "gemm_tcgen05_grouped: unknown activation %d", act);
+    }
     TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_tcgen05_grouped: unknown activation %d", act);
     if (gated && act == kActGeluTanh)
         return launch_tcgen05<true, 1, kActGeluTanh>(mx, mw, y, rows, n, K, n / 2, 1, error_word, stream, grouped, max_tiles);

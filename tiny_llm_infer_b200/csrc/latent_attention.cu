@@ -16,8 +16,9 @@
 //   heads_gate         per token: out[t, h, :] = x[h, t, :] * sigmoid(gate[t, h, :]), the batched product's
 //                      [heads, tokens, width] order turned back into rows.
 //
-// The rotation pairs neighbours (2i, 2i + 1) of the first `rot_dims` elements: (u, v) -> (u cos a - v sin a,
-// v cos a + u sin a) * mag, a = position * freq_i as a float32 product, cos and sin from the precise functions.
+// The rotation pairs neighbours (2i, 2i + 1) of the first `rot_dims` elements, or, `half_pairs`, elements i and
+// i + rot_dims / 2: (u, v) -> (u cos a - v sin a, v cos a + u sin a) * mag, a = position * freq_i as a float32
+// product, cos and sin from the precise functions.
 #include "common.cuh"
 
 namespace tllm {
@@ -28,7 +29,7 @@ __global__ void latent_norm_store_kernel(const T* proj, int ld, int q_rank, int 
                                          float eps, const float* __restrict__ freq, float mag,
                                          const int* __restrict__ positions, const int* __restrict__ token_slot,
                                          const int* __restrict__ block_table, int max_pages, int page_size,
-                                         T* plane, long long page_stride, T* cq, int store) {
+                                         T* plane, long long page_stride, T* cq, int store, int half_pairs) {
     __shared__ float scratch[32];
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
@@ -61,18 +62,19 @@ __global__ void latent_norm_store_kernel(const T* proj, int ld, int q_rank, int 
     for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
         const float a = (float)pos * freq[i];
         const float cs = cosf(a) * mag, sn = sinf(a) * mag;
-        const float u = to_f32<T>(kr[2 * i]), v = to_f32<T>(kr[2 * i + 1]);
-        dst[rank + 2 * i] = from_f32<T>(u * cs - v * sn);
-        dst[rank + 2 * i + 1] = from_f32<T>(v * cs + u * sn);
+        const int iu = half_pairs ? i : 2 * i, iv = half_pairs ? i + rot_dims / 2 : 2 * i + 1;
+        const float u = to_f32<T>(kr[iu]), v = to_f32<T>(kr[iv]);
+        dst[rank + iu] = from_f32<T>(u * cs - v * sn);
+        dst[rank + iv] = from_f32<T>(v * cs + u * sn);
     }
     for (int e = rot_dims + threadIdx.x; e < rot; e += blockDim.x) dst[rank + e] = kr[e];
 }
 
-// q [T, heads, plain + rot]; lat [heads, T, rank]; out [T, heads, rank + rot]
+// q [T, heads, plain + rot] in rows of ldq elements; lat [heads, T, rank]; out [T, heads, rank + rot]
 template <typename T>
-__global__ void latent_query_kernel(const T* q, const T* lat, int heads, int plain, int rot, int rot_dims, int rank,
+__global__ void latent_query_kernel(const T* q, int ldq, const T* lat, int heads, int plain, int rot, int rot_dims, int rank,
                                     const float* __restrict__ freq, float mag, const int* __restrict__ positions,
-                                    const int* __restrict__ token_slot, int tokens, T* out) {
+                                    const int* __restrict__ token_slot, int tokens, T* out, int half_pairs) {
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const int width = rank + rot;
@@ -91,20 +93,22 @@ __global__ void latent_query_kernel(const T* q, const T* lat, int heads, int pla
             continue;
         }
         const int d = e - rank;
-        const T* src = q + ((size_t)t * heads + h) * (plain + rot) + plain;
+        const T* src = q + (size_t)t * ldq + (size_t)h * (plain + rot) + plain;
         if (d >= rot_dims) { dst[e] = src[d]; continue; }
-        const int pair = d >> 1;
+        const int hw = rot_dims >> 1;
+        const int pair = half_pairs ? (d < hw ? d : d - hw) : d >> 1;
+        const bool second = half_pairs ? d >= hw : (d & 1);
         const float a = (float)pos * freq[pair];
         const float cs = cosf(a) * mag, sn = sinf(a) * mag;
-        const float u = to_f32<T>(src[2 * pair]), v = to_f32<T>(src[2 * pair + 1]);
-        dst[e] = from_f32<T>((d & 1) ? v * cs + u * sn : u * cs - v * sn);
+        const float u = to_f32<T>(src[half_pairs ? pair : 2 * pair]), v = to_f32<T>(src[half_pairs ? pair + hw : 2 * pair + 1]);
+        dst[e] = from_f32<T>(second ? v * cs + u * sn : u * cs - v * sn);
     }
 }
 
-// x [heads, T, width]; gate rows of stride ldg; out [T, heads * width]
+// x [heads, T, width]; gate rows of stride ldg, one number per element or, `per_head`, one per head; out [T, heads * width]
 template <typename T>
 __global__ void heads_gate_kernel(const T* x, const T* gate, int ldg, int heads, int width, int tokens,
-                                  const int* __restrict__ token_slot, T* out) {
+                                  const int* __restrict__ token_slot, T* out, int per_head) {
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const bool pad = token_slot != nullptr && token_slot[t] < 0;
@@ -115,7 +119,7 @@ __global__ void heads_gate_kernel(const T* x, const T* gate, int ldg, int heads,
         float v = 0.0f;
         if (!pad) {
             v = to_f32<T>(x[((size_t)h * tokens + t) * width + e]);
-            if (gate != nullptr) v *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * ldg + i])));
+            if (gate != nullptr) v *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * ldg + (per_head ? h : i)])));
         }
         out[(size_t)t * heads * width + i] = from_f32<T>(v);
     }
@@ -139,7 +143,7 @@ int tllm_latent_norm_store(const void* proj, int ld, int dtype, int q_rank, int 
                            const float* q_gain, const float* c_gain, float eps, const float* freq, float mag,
                            const int* positions, const int* token_slot, const int* block_table, int max_pages,
                            int page_size, void* plane, long long page_stride, void* cq, int store, int tokens,
-                           cudaStream_t stream) {
+                           int half_pairs, cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && q_rank >= 0 && rank > 0 && rot >= 0 && rot_dims >= 0 && rot_dims <= rot && rot_dims % 2 == 0,
                  "latent_norm_store: bad sizes");
     TLLM_REQUIRE(ld >= q_rank + rank + rot && eps > 0.0f, "latent_norm_store: rows too short");
@@ -149,7 +153,7 @@ int tllm_latent_norm_store(const void* proj, int ld, int dtype, int q_rank, int 
 #define STORE(T)                                                                                                   \
     launch_pdl(kPdlQk, latent_norm_store_kernel<T>, dim3(tokens), dim3(128), 0, stream, (const T*)proj, ld, q_rank, \
                rank, rot, rot_dims, q_gain, c_gain, eps, freq, mag, positions, token_slot, block_table, max_pages,  \
-               page_size, (T*)plane, page_stride, (T*)cq, store)
+               page_size, (T*)plane, page_stride, (T*)cq, store, half_pairs)
     if (dtype == kBF16) STORE(bf16);
     else if (dtype == kF32) STORE(float);
     else TLLM_REQUIRE(false, "latent_norm_store: unknown dtype %d", dtype);
@@ -157,34 +161,35 @@ int tllm_latent_norm_store(const void* proj, int ld, int dtype, int q_rank, int 
     return finish_launch("latent_norm_store");
 }
 
-int tllm_latent_query(const void* q, const void* lat, int dtype, int heads, int plain, int rot, int rot_dims, int rank,
+int tllm_latent_query(const void* q, int ldq, const void* lat, int dtype, int heads, int plain, int rot, int rot_dims, int rank,
                       const float* freq, float mag, const int* positions, const int* token_slot, int tokens, void* out,
-                      cudaStream_t stream) {
+                      int half_pairs, cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && heads > 0 && plain >= 0 && rot >= 0 && rank > 0 && rot_dims <= rot && rot_dims % 2 == 0,
                  "latent_query: bad sizes");
+    TLLM_REQUIRE(ldq >= heads * (plain + rot), "latent_query: rows of %d are too short", ldq);
     if (tokens == 0) return 0;
     const int split = row_split(tokens, heads * (rank + rot));
     if (dtype == kBF16)
-        launch_pdl(kPdlQk, latent_query_kernel<bf16>, dim3(tokens, split), dim3(256), 0, stream, (const bf16*)q, (const bf16*)lat, heads,
-                   plain, rot, rot_dims, rank, freq, mag, positions, token_slot, tokens, (bf16*)out);
+        launch_pdl(kPdlQk, latent_query_kernel<bf16>, dim3(tokens, split), dim3(256), 0, stream, (const bf16*)q, ldq, (const bf16*)lat, heads,
+                   plain, rot, rot_dims, rank, freq, mag, positions, token_slot, tokens, (bf16*)out, half_pairs);
     else if (dtype == kF32)
-        launch_pdl(kPdlQk, latent_query_kernel<float>, dim3(tokens, split), dim3(256), 0, stream, (const float*)q, (const float*)lat, heads,
-                   plain, rot, rot_dims, rank, freq, mag, positions, token_slot, tokens, (float*)out);
+        launch_pdl(kPdlQk, latent_query_kernel<float>, dim3(tokens, split), dim3(256), 0, stream, (const float*)q, ldq, (const float*)lat, heads,
+                   plain, rot, rot_dims, rank, freq, mag, positions, token_slot, tokens, (float*)out, half_pairs);
     else TLLM_REQUIRE(false, "latent_query: unknown dtype %d", dtype);
     return finish_launch("latent_query");
 }
 
 int tllm_heads_gate(const void* x, const void* gate, int ldg, int dtype, int heads, int width, int tokens,
-                    const int* token_slot, void* out, cudaStream_t stream) {
-    TLLM_REQUIRE(tokens >= 0 && heads > 0 && width > 0 && (gate == nullptr || ldg >= heads * width), "heads_gate: bad sizes");
+                    const int* token_slot, void* out, int per_head, cudaStream_t stream) {
+    TLLM_REQUIRE(tokens >= 0 && heads > 0 && width > 0 && (gate == nullptr || ldg >= (per_head ? heads : heads * width)), "heads_gate: bad sizes");
     if (tokens == 0) return 0;
     const int split = row_split(tokens, heads * width);
     if (dtype == kBF16)
         launch_pdl(kPdlOther, heads_gate_kernel<bf16>, dim3(tokens, split), dim3(256), 0, stream, (const bf16*)x, (const bf16*)gate, ldg,
-                   heads, width, tokens, token_slot, (bf16*)out);
+                   heads, width, tokens, token_slot, (bf16*)out, per_head);
     else if (dtype == kF32)
         launch_pdl(kPdlOther, heads_gate_kernel<float>, dim3(tokens, split), dim3(256), 0, stream, (const float*)x, (const float*)gate, ldg,
-                   heads, width, tokens, token_slot, (float*)out);
+                   heads, width, tokens, token_slot, (float*)out, per_head);
     else TLLM_REQUIRE(false, "heads_gate: unknown dtype %d", dtype);
     return finish_launch("heads_gate");
 }

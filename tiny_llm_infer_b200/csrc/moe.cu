@@ -4,6 +4,9 @@
 //
 //   route    z [T, E] float32 router logits -> the `top` experts with the largest z per token
 //            (lowest index first on ties) and their weights, sigmoid(z) or softmax over the chosen;
+//            `route_grouped`: scores over all experts (softmax or sigmoid), a learned correction added for
+//            the choice only, experts in equal groups of neighbours of which only the best few may be
+//            chosen from, the weights the chosen experts' scores as they are;
 //   plan     counting sort of the T * top assignments by expert: offsets per expert, the row every
 //            assignment gets, and the list of (expert, first row) tiles of the rows (64 for the mma.sync
 //            products of this file, 128 for the grouped tcgen05 product);
@@ -14,7 +17,8 @@
 //            registers), float32 and odd sizes run one thread per output with the sum over k in order;
 //            steps with many rows take the grouped form of the tcgen05 product instead (gemm_tcgen05.cu),
 //            which reads its rows by TMA: `gather` lays the token rows out in the plan's order first;
-//   combine  out[t] = shared[t] + sum over the token's assignments of (weight *) y[row], in float32.
+//   combine  out[t] = shared[t] + sum over the token's assignments of (weight *) y[row], in float32; an
+//            assignment to an expert past the last real one (an identity expert) adds the token's input instead.
 //
 // A row's result does not depend on which other rows share its tile or its expert.
 #include "common.cuh"
@@ -60,10 +64,89 @@ __global__ void moe_route_kernel(const float* z, int tokens, int experts, int to
         for (int k = 0; k < top; ++k) weights[(size_t)warp * top + k] /= denom;
 }
 
+// Routing over scores of all experts.  One warp per token, E <= 1024; shared memory per warp: E choice scores,
+// then one number per group.  score s = softmax(z) over all E (score_mode 1) or sigmoid(z) (0); choice = s +
+// correction (if given); a group's score is its largest choice; only experts of the `keep` best groups can be
+// chosen (lowest index first on ties, for groups and experts alike); weights are the scores s themselves.
+__global__ void moe_route_grouped_kernel(const float* z, int tokens, int experts, int top, int score_mode,
+                                         const float* __restrict__ correction, int groups, int keep,
+                                         int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float route_smem[];
+    TLLM_PDL_ENTER();
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = blockIdx.x * (blockDim.x >> 5) + wib;
+    if (warp >= tokens) return;
+    float* choice = route_smem + (size_t)wib * (experts + groups);
+    float* gscore = choice + experts;
+    const float* row = z + (size_t)warp * experts;
+    float top_z = -INFINITY;
+    for (int e = lane; e < experts; e += 32) top_z = fmaxf(top_z, row[e]);
+    top_z = warp_max(top_z);
+    float denom = 0.0f;
+    if (score_mode == 1) {
+        for (int e = lane; e < experts; e += 32) denom += expf(row[e] - top_z);
+        denom = warp_sum(denom);
+    }
+    auto score_of = [&](int e) -> float {
+        return score_mode == 1 ? expf(row[e] - top_z) / denom : 1.0f / (1.0f + expf(-row[e]));
+    };
+    for (int e = lane; e < experts; e += 32) choice[e] = score_of(e) + (correction != nullptr ? correction[e] : 0.0f);
+    __syncwarp();
+    const int size = experts / groups;
+    if (groups > 1) {
+        for (int g = lane; g < groups; g += 32) {
+            float m = -INFINITY;
+            for (int i = 0; i < size; ++i) m = fmaxf(m, choice[g * size + i]);
+            gscore[g] = m;
+        }
+        __syncwarp();
+        // the best `keep` groups stay; a group that is taken is marked by a NaN-free sentinel: +inf
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int best_g = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = gscore[g];
+                if (v == INFINITY) continue;                   // already kept
+                if (best_g == 0x7fffffff || v > best) { best = v; best_g = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+                if (og != 0x7fffffff && (best_g == 0x7fffffff || ov > best || (ov == best && og < best_g))) { best = ov; best_g = og; }
+            }
+            if (lane == 0 && best_g != 0x7fffffff) gscore[best_g] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < experts; e += 32)
+            if (gscore[e / size] != INFINITY) choice[e] = -INFINITY;
+        __syncwarp();
+    }
+    uint32_t taken = 0;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int c = 0, e = lane; e < experts; ++c, e += 32) {
+            if (taken & (1u << c)) continue;
+            const float v = choice[e];
+            if (best_e == 0x7fffffff || v > best) { best = v; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (oe != 0x7fffffff && (best_e == 0x7fffffff || ov > best || (ov == best && oe < best_e))) { best = ov; best_e = oe; }
+        }
+        if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
+        if (lane == 0) { ids[(size_t)warp * top + k] = best_e; weights[(size_t)warp * top + k] = score_of(best_e); }
+    }
+}
+
 // ---------------------------------------------------------------- plan
 // One block.  ints: offsets [E + 1] | n_tiles [1] | row_of [n] | src_of [n] | expert_of_row [n] |
 // tile_expert [max tiles] | tile_row0 [max tiles].
-__global__ void moe_plan_kernel(const int* ids, int n, int experts, int tile_rows, int* offsets, int* n_tiles,
+// Experts from `real` on have no matrices (their assignments get rows, and no tiles).
+__global__ void moe_plan_kernel(const int* ids, int n, int experts, int real, int tile_rows, int* offsets, int* n_tiles,
                                 int* row_of, int* src_of, int* expert_of_row, int* tile_expert, int* tile_row0) {
     extern __shared__ int plan_smem[];
     TLLM_PDL_ENTER();
@@ -77,7 +160,8 @@ __global__ void moe_plan_kernel(const int* ids, int n, int experts, int tile_row
         int at = 0, tiles = 0;
         for (int e = 0; e < experts; ++e) {
             offsets[e] = cursor[e] = at;
-            for (int r = at; r < at + count[e]; r += tile_rows) { tile_expert[tiles] = e; tile_row0[tiles] = r; ++tiles; }
+            if (e < real)
+                for (int r = at; r < at + count[e]; r += tile_rows) { tile_expert[tiles] = e; tile_row0[tiles] = r; ++tiles; }
             at += count[e];
         }
         offsets[experts] = at;
@@ -115,16 +199,17 @@ __device__ __forceinline__ int gate_up_row(int col, bool up, int n, int interlea
     return up ? n + col : col;
 }
 
-// GATED: a block's 64 weight rows are, per warp column of 32, sixteen gate rows and the sixteen up rows
+// MODE 1 (gated): a block's 64 weight rows are, per warp column of 32, sixteen gate rows and the sixteen up rows
 // that belong to them; the block writes 32 columns of act(gate) * up in bfloat16.  Otherwise 64 columns
-// of the plain product in float32.
-template <bool GATED, bool GATHER>
+// of the plain product, in float32 (MODE 0) or, with the activation on every output, in bfloat16 (MODE 2).
+template <int MODE, bool GATHER>
 __global__ void __launch_bounds__(kGThreads)
 moe_grouped_mma_kernel(const bf16* A, int lda, const int* src_of, const float* weight_of, int top,
                        const bf16* W, long long w_stride, const int* tile_expert, const int* tile_row0,
                        const int* n_tiles, const int* offsets, int N, int K, int act, int interleaved, void* C) {
     __shared__ __align__(16) bf16 As[2][kGM][kGK + kGPad];
     __shared__ __align__(16) bf16 Bs[2][kGN][kGK + kGPad];
+    constexpr bool GATED = MODE == 1;
     TLLM_PDL_ENTER();
     if ((int)blockIdx.y >= *n_tiles) return;
     const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y];
@@ -239,6 +324,14 @@ moe_grouped_mma_kernel(const bf16* A, int lda, const int* src_of, const float* w
                     if (col < N) out[col] = __float2bfloat16_rn(gate_act(g0, act) * u0);
                     if (col + 1 < N) out[col + 1] = __float2bfloat16_rn(gate_act(g1, act) * u1);
                 }
+            } else if (MODE == 2) {
+                bf16* out = (bf16*)C + (size_t)(row0 + r) * N;
+#pragma unroll
+                for (int ni = 0; ni < 4; ++ni) {
+                    const int col = n0 + wn * 32 + ni * 8 + (lane & 3) * 2;
+                    if (col < N) out[col] = __float2bfloat16_rn(gate_act(acc[mi][ni][hrow * 2], act));
+                    if (col + 1 < N) out[col + 1] = __float2bfloat16_rn(gate_act(acc[mi][ni][hrow * 2 + 1], act));
+                }
             } else {
                 float* out = (float*)C + (size_t)(row0 + r) * N;
 #pragma unroll
@@ -252,14 +345,17 @@ moe_grouped_mma_kernel(const bf16* A, int lda, const int* src_of, const float* w
 }
 
 // ---------------------------------------------------------------- products, plain
-// One thread per output: float32 sum over k in order.  TA: storage type of A and of a gated result.
-template <typename TA, bool GATED, bool GATHER>
+// One thread per output: float32 sum over k in order.  TA: storage type of A and of a gated (MODE 1) or
+// activated (MODE 2) result; MODE 0 leaves float32.
+template <typename TA, int MODE, bool GATHER>
 __global__ void moe_grouped_plain_kernel(const TA* A, int lda, const int* src_of, const float* weight_of, int top,
                                          const TA* W, long long w_stride, const int* expert_of_row, int rows,
-                                         int N, int K, int act, int interleaved, void* C) {
+                                         int N, int K, int act, int interleaved, int real, void* C) {
+    constexpr bool GATED = MODE == 1;
     TLLM_PDL_ENTER();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)rows * N) return;
+    if (expert_of_row[idx / N] >= real) return;      // a row of an expert without matrices
     const int r = (int)(idx / N), n = (int)(idx % N);
     const TA* a;
     float w = 1.0f;
@@ -283,7 +379,8 @@ __global__ void moe_grouped_plain_kernel(const TA* A, int lda, const int* src_of
         ((TA*)C)[idx] = from_f32<TA>(gate_act(g, act) * u);
     } else {
         for (int k = 0; k < K; ++k) g += to_f32<TA>(from_f32<TA>(to_f32<TA>(a[k]) * w)) * to_f32<TA>(wg[k]);
-        ((float*)C)[idx] = g;
+        if (MODE == 2) ((TA*)C)[idx] = from_f32<TA>(gate_act(g, act));
+        else ((float*)C)[idx] = g;
     }
 }
 
@@ -306,9 +403,12 @@ __global__ void moe_gather_kernel(const bf16* x, const int* src_of, const float*
 }
 
 // ---------------------------------------------------------------- combine
+// x, expert_of_row, real: where given, an assignment whose expert is `real` or later adds the token's own row
+// of x (times the weight) instead of a row of y.
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* y, const int* row_of, const float* weight_of, int top,
-                                   const T* shared, T* out, int width, size_t total) {
+                                   const T* shared, T* out, int width, size_t total, const T* x,
+                                   const int* expert_of_row, int real) {
     TLLM_PDL_ENTER();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -316,7 +416,9 @@ __global__ void moe_combine_kernel(const TY* y, const int* row_of, const float* 
         const size_t t = idx / width, i = idx - t * width;
         float v = shared != nullptr ? to_f32<T>(shared[idx]) : 0.0f;
         for (int k = 0; k < top; ++k) {
-            const float yv = to_f32<TY>(y[(size_t)row_of[t * top + k] * width + i]);
+            const int row = row_of[t * top + k];
+            const float yv = (x != nullptr && expert_of_row[row] >= real) ? to_f32<T>(x[idx])
+                                                                         : to_f32<TY>(y[(size_t)row * width + i]);
             v += weight_of != nullptr ? weight_of[t * top + k] * yv : yv;
         }
         out[idx] = from_f32<T>(v);
@@ -342,22 +444,42 @@ int tllm_moe_route(const float* z, int tokens, int experts, int top, int softmax
     return finish_launch("moe_route");
 }
 
-int tllm_moe_plan(const int* ids, int n, int experts, int tile_rows, int* offsets, int* n_tiles, int* row_of,
+// score_mode: 0 sigmoid(z), 1 softmax(z) over all experts.  correction [experts] float32 or null.  groups equal
+// groups of neighbouring experts, of which the `keep` with the best member may be chosen from.
+int tllm_moe_route_grouped(const float* z, int tokens, int experts, int top, int score_mode, const float* correction,
+                           int groups, int keep, int* ids, float* weights, cudaStream_t stream) {
+    TLLM_REQUIRE(tokens >= 0 && experts > 0 && experts <= 1024 && top > 0 && top <= experts,
+                 "moe_route_grouped: %d experts, top %d", experts, top);
+    TLLM_REQUIRE(score_mode == 0 || score_mode == 1, "moe_route_grouped: unknown scores %d", score_mode);
+    TLLM_REQUIRE(groups > 0 && experts % groups == 0 && keep > 0 && keep <= groups && keep * (experts / groups) >= top,
+                 "moe_route_grouped: %d groups of %d experts, %d kept, top %d", groups, experts, keep, top);
+    if (tokens == 0) return 0;
+    const int warps = 4;
+    launch_pdl(kPdlOther, moe_route_grouped_kernel, dim3((tokens + warps - 1) / warps), dim3(warps * 32),
+               (size_t)warps * (experts + groups) * sizeof(float), stream, z, tokens, experts, top, score_mode,
+               correction, groups, keep, ids, weights);
+    return finish_launch("moe_route_grouped");
+}
+
+int tllm_moe_plan(const int* ids, int n, int experts, int real, int tile_rows, int* offsets, int* n_tiles, int* row_of,
                   int* src_of, int* expert_of_row, int* tile_expert, int* tile_row0, cudaStream_t stream) {
-    TLLM_REQUIRE(n > 0 && experts > 0 && experts <= 4096 && tile_rows > 0, "moe_plan: bad sizes");
+    TLLM_REQUIRE(n > 0 && experts > 0 && experts <= 4096 && tile_rows > 0 && real >= 0 && real <= experts, "moe_plan: bad sizes");
     launch_pdl(kPdlOther, moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), stream,
-               ids, n, experts, tile_rows, offsets, n_tiles, row_of, src_of, expert_of_row, tile_expert, tile_row0);
+               ids, n, experts, real, tile_rows, offsets, n_tiles, row_of, src_of, expert_of_row, tile_expert, tile_row0);
     return finish_launch("moe_plan");
 }
 
-// rows: all rows of the plan (tokens * top); max_tiles: bound on the plan's tiles.  gated: W is
+// rows: all rows of the plan (tokens * top); max_tiles: bound on the plan's tiles.  mode 1 (gated): W is
 // [experts][2 N][K] (gate rows, then up rows) and C [rows, N] in the storage type; else W is
-// [experts][N][K] and C [rows, N] float32.  gather: A is [tokens, K] and row r reads token
-// src_of[r] / top, scaled by weight_of[src_of[r]] if that is given.
+// [experts][N][K] and C [rows, N] float32 (mode 0) or act(.) in the storage type (mode 2).  gather: A is
+// [tokens, K] and row r reads token src_of[r] / top, scaled by weight_of[src_of[r]] if that is given.
+// real: experts that have matrices (rows of later ones are left alone).
 int tllm_moe_grouped(const void* A, int lda, const int* src_of, const float* weight_of, int top, const void* W,
                      long long w_stride, const int* tile_expert, const int* tile_row0, const int* n_tiles,
                      const int* offsets, const int* expert_of_row, int rows, int max_tiles, int N, int K,
-                     int dtype, int gated, int gather, int act, int interleaved, void* C, cudaStream_t stream) {
+                     int dtype, int mode, int gather, int act, int interleaved, int real, void* C, cudaStream_t stream) {
+    const bool gated = mode == 1;
+    TLLM_REQUIRE(mode >= 0 && mode <= 2, "moe_grouped: unknown mode %d", mode);
     TLLM_REQUIRE(!interleaved || (gated && N % 8 == 0), "moe_grouped: interleaved gate and up rows need N %% 8 == 0");
     TLLM_REQUIRE(rows >= 0 && N > 0 && K > 0 && max_tiles > 0, "moe_grouped: bad sizes");
     TLLM_REQUIRE(dtype == kBF16 || dtype == kF32, "moe_grouped: unknown dtype %d", dtype);
@@ -370,10 +492,12 @@ int tllm_moe_grouped(const void* A, int lda, const int* src_of, const float* wei
 #define MMA(G, H)                                                                                              \
     launch_pdl(kPdlOther, moe_grouped_mma_kernel<G, H>, grid, block, 0, stream, (const bf16*)A, lda, src_of,    \
                weight_of, top, (const bf16*)W, w_stride, tile_expert, tile_row0, n_tiles, offsets, N, K, act, interleaved, C)
-        if (gated && gather) MMA(true, true);
-        else if (gated) MMA(true, false);
-        else if (gather) MMA(false, true);
-        else MMA(false, false);
+        if (gated && gather) MMA(1, true);
+        else if (gated) MMA(1, false);
+        else if (mode == 2 && gather) MMA(2, true);
+        else if (mode == 2) MMA(2, false);
+        else if (gather) MMA(0, true);
+        else MMA(0, false);
 #undef MMA
         return finish_launch("moe_grouped");
     }
@@ -381,18 +505,19 @@ int tllm_moe_grouped(const void* A, int lda, const int* src_of, const float* wei
     const dim3 grid((unsigned)((total + 255) / 256)), block(256);
 #define PLAIN(T, G, H)                                                                                          \
     launch_pdl(kPdlOther, moe_grouped_plain_kernel<T, G, H>, grid, block, 0, stream, (const T*)A, lda, src_of,  \
-               weight_of, top, (const T*)W, w_stride, expert_of_row, rows, N, K, act, interleaved, C)
-    if (dtype == kBF16) {
-        if (gated && gather) PLAIN(bf16, true, true);
-        else if (gated) PLAIN(bf16, true, false);
-        else if (gather) PLAIN(bf16, false, true);
-        else PLAIN(bf16, false, false);
-    } else {
-        if (gated && gather) PLAIN(float, true, true);
-        else if (gated) PLAIN(float, true, false);
-        else if (gather) PLAIN(float, false, true);
-        else PLAIN(float, false, false);
-    }
+               weight_of, top, (const T*)W, w_stride, expert_of_row, rows, N, K, act, interleaved, real, C)
+#define PLAIN_T(T)                                         \
+    do {                                                   \
+        if (gated && gather) PLAIN(T, 1, true);            \
+        else if (gated) PLAIN(T, 1, false);                \
+        else if (mode == 2 && gather) PLAIN(T, 2, true);   \
+        else if (mode == 2) PLAIN(T, 2, false);            \
+        else if (gather) PLAIN(T, 0, true);                \
+        else PLAIN(T, 0, false);                           \
+    } while (0)
+    if (dtype == kBF16) PLAIN_T(bf16);
+    else PLAIN_T(float);
+#undef PLAIN_T
 #undef PLAIN
     return finish_launch("moe_grouped");
 }
@@ -409,9 +534,12 @@ int tllm_moe_gather(const void* x, const int* src_of, const float* weight_of, in
     return finish_launch("moe_gather");
 }
 
+// x, expert_of_row, real: all or none; assignments to experts from `real` on add the token's row of x.
 int tllm_moe_combine(const void* y, int y_dtype, const int* row_of, const float* weight_of, int top, const void* shared,
-                     void* out, int dtype, int tokens, int width, cudaStream_t stream) {
+                     void* out, int dtype, int tokens, int width, const void* x, const int* expert_of_row, int real,
+                     cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && width > 0 && top > 0, "moe_combine: bad sizes");
+    TLLM_REQUIRE(x == nullptr || expert_of_row != nullptr, "moe_combine: identity experts need the rows' experts");
     const size_t total = (size_t)tokens * width;
     if (total == 0) return 0;
     const int block = 256;
@@ -419,13 +547,13 @@ int tllm_moe_combine(const void* y, int y_dtype, const int* row_of, const float*
     const int grid = (int)(g > 148 * 16 ? 148 * 16 : g);
     if (dtype == kBF16 && y_dtype == kBF16)
         launch_pdl(kPdlOther, moe_combine_kernel<bf16, bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)y, row_of, weight_of, top,
-                   (const bf16*)shared, (bf16*)out, width, total);
+                   (const bf16*)shared, (bf16*)out, width, total, (const bf16*)x, expert_of_row, real);
     else if (dtype == kBF16 && y_dtype == kF32)
         launch_pdl(kPdlOther, moe_combine_kernel<bf16, float>, dim3(grid), dim3(block), 0, stream, (const float*)y, row_of, weight_of, top,
-                   (const bf16*)shared, (bf16*)out, width, total);
+                   (const bf16*)shared, (bf16*)out, width, total, (const bf16*)x, expert_of_row, real);
     else if (dtype == kF32 && y_dtype == kF32)
         launch_pdl(kPdlOther, moe_combine_kernel<float, float>, dim3(grid), dim3(block), 0, stream, (const float*)y, row_of, weight_of, top,
-                   (const float*)shared, (float*)out, width, total);
+                   (const float*)shared, (float*)out, width, total, (const float*)x, expert_of_row, real);
     else
         TLLM_REQUIRE(false, "moe_combine: unknown dtypes %d, %d", dtype, y_dtype);
     return finish_launch("moe_combine");

@@ -1,3 +1,3 @@
 """Architectures.  Importing this package registers them (see ``config.base``)."""
-from . import kaketar, panolorn, qwen3, tetodra  # noqa: F401
+from . import kaketar, panolorn, pevolorn, qwen3, tetodra  # noqa: F401
 from .model import Model, expected_tensors

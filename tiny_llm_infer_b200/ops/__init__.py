@@ -64,13 +64,13 @@ def _declare(h) -> None:
         "tllm_embedding": [vp, vp, i32, vp, i32, i32, i32, f32, vp],
         "tllm_postnorm_add_rmsnorm": [vp, vp, vp, f32, vp, i32, f32, vp, i32, vp, i32, i32, vp],
         "tllm_qkv_unit_store": [vp, i32, vp, vp, f32, i32, vp, vp, vp, i32, i32, vp, vp, i64, vp, i32, i32,
-                                i32, i32, i32, i32, i32, vp, i32, f32, i32, i32, vp],
+                                i32, i32, i32, i32, i32, vp, i32, f32, i32, i32, vp, vp],
         "tllm_attention_biased_general": [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32,
-                                          f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, vp, vp],
+                                          f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, i32, vp, vp],
         "tllm_attention_biased_prefill": [vp, vp, vp, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                                          f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, vp, vp],
+                                          f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, i32, vp, vp],
         "tllm_attention_biased_decode": [vp, vp, vp, i64, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                                         f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, i32, vp, vp, vp],
+                                         f32, f32, i32, i32, i32, vp, vp, vp, i32, i32, vp, i32, i32, i32, vp, vp, vp],
         "tllm_scaled_add_layernorm": [vp, vp, vp, i32, vp, i32, f32, vp, i32, vp, i32, i32, vp],
         "tllm_linear_prepare": [vp, i32, i32, vp, i32, vp, i32, f32, vp, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp,
                                 i32, vp],
@@ -84,15 +84,20 @@ def _declare(h) -> None:
         "tllm_delta_finish": [vp, vp, i32, i32, vp, f32, vp, i32, i32, i32, i32, i32, vp, i32, vp, i32, i32, vp, i64,
                               vp, i32, i32, vp],
         "tllm_latent_norm_store": [vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, vp, f32, vp, vp, vp, i32, i32,
-                                   vp, i64, vp, i32, i32, vp],
-        "tllm_latent_query": [vp, vp, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, vp],
-        "tllm_heads_gate": [vp, vp, i32, i32, i32, i32, i32, vp, vp, vp],
+                                   vp, i64, vp, i32, i32, i32, vp],
+        "tllm_latent_query": [vp, i32, vp, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, i32, vp],
+        "tllm_heads_gate": [vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp],
         "tllm_moe_route": [vp, i32, i32, i32, i32, vp, vp, vp],
-        "tllm_moe_plan": [vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp],
+        "tllm_moe_route_grouped": [vp, i32, i32, i32, i32, vp, i32, i32, vp, vp, vp],
+        "tllm_moe_plan": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp],
         "tllm_moe_grouped": [vp, i32, vp, vp, i32, vp, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
-                             i32, i32, i32, vp, vp],
+                             i32, i32, i32, i32, vp, vp],
         "tllm_moe_gather": [vp, vp, vp, i32, vp, i32, i32, vp],
-        "tllm_moe_combine": [vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, vp],
+        "tllm_moe_combine": [vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, vp, vp, i32, vp],
+        "tllm_sum_rmsnorm": [vp, vp, vp, i32, f32, vp, vp, f32, vp, i32, i32, i32, vp],
+        "tllm_ssd_prepare": [vp, i32, i32, vp, vp, i32, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp,
+                             vp, vp, i32, vp],
+        "tllm_ssd_finish": [vp, vp, vp, i32, i32, vp, f32, i32, vp, i32, i32, i32, i32, vp, i64, i64, vp, vp],
         "tllm_gemm_tcgen05_grouped": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp],
         "tllm_add_rmsnorm": [vp, vp, vp, i32, f32, vp, i32, vp, i32, i32, vp],
         "tllm_swiglu": [vp, vp, i32, i32, i32, i32, i32, vp],
@@ -227,6 +232,26 @@ def scaled_add_layernorm(h: torch.Tensor, deltas, scales, gain: torch.Tensor, ep
     _check(lib().tllm_scaled_add_layernorm(_p(h), ctypes.cast(dp, ctypes.c_void_p), ctypes.cast(sp, ctypes.c_void_p), n,
                                            _p(gain), _dt(gain), float(eps), _p(out), _dt(out), _p(rows), n_out,
                                            h.shape[-1], _stream()), "scaled_add_layernorm")
+    return out
+
+
+def sum_rmsnorm(h: torch.Tensor, deltas, coefs, alpha: float, gain: torch.Tensor, eps: float, out: torch.Tensor,
+                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h <- gain * v / sqrt(mean(v^2) + eps) with v = alpha * h + sum_i coefs[i] * deltas[i] (+ bias), for every row:
+    the norm of a weighted sum becomes the stream itself (float32); ``out`` receives the new stream in the storage
+    type.  ``deltas[i]`` [T, width] in the storage type with one float each (at most four), ``gain`` and ``bias``
+    float32 vectors."""
+    _cuda(h, gain, out, bias, *deltas)
+    assert h.dtype == torch.float32 and gain.dtype == torch.float32 and len(deltas) == len(coefs) <= 4
+    assert out.shape == h.shape and gain.numel() == h.shape[1] and (bias is None or (bias.dtype == torch.float32 and bias.numel() == h.shape[1]))
+    for d in deltas:
+        assert d.dtype == out.dtype and d.shape == h.shape
+    n = len(deltas)
+    dp = (ctypes.c_void_p * 4)(*[d.data_ptr() for d in deltas])
+    cp = (ctypes.c_float * 4)(*[float(c) for c in coefs])
+    _check(lib().tllm_sum_rmsnorm(_p(h), ctypes.cast(dp, ctypes.c_void_p), ctypes.cast(cp, ctypes.c_void_p), n, float(alpha),
+                                  _p(bias), _p(gain), float(eps), _p(out), _dt(out), h.shape[0], h.shape[1], _stream()),
+           "sum_rmsnorm")
     return out
 
 
@@ -576,12 +601,19 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, sh
     return y
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[T, N] = x[T, K] . weight[N, K]^T with float32 accumulation.  A weight kept in
-    float32 is multiplied in float32 whatever the activations are stored in."""
+    float32 is multiplied in float32 whatever the activations are stored in.  ``bias`` [N] (the weight's type) is
+    added in the library product's epilogue."""
     if not x.is_cuda:
         raise KernelError("linear takes CUDA tensors")
     want = out_dtype or x.dtype
+    if bias is not None:
+        if weight.dtype == torch.float32 and (torch.backends.cuda.matmul.allow_tf32 or torch.get_float32_matmul_precision() != "highest"):
+            raise KernelError("float32 products need the reduced-precision matrix modes off")
+        y = torch.addmm(bias.to(weight.dtype), cast(x, weight.dtype), weight.t())
+        return y if want == y.dtype else cast(y, want)
     if weight.dtype == torch.float32:
         if torch.backends.cuda.matmul.allow_tf32 or torch.get_float32_matmul_precision() != "highest":
             raise KernelError("float32 products need the reduced-precision matrix modes off")
@@ -656,15 +688,18 @@ def qkv_unit_store(proj: torch.Tensor, q_out: torch.Tensor, positions, token_slo
                    q_heads: int, kv_heads: int, dk: int, dv: int, eps: Optional[float],
                    q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
                    store: bool = True, inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0,
-                   q_temperature=None, values_are_keys: bool = False) -> None:
+                   q_temperature=None, values_are_keys: bool = False, bias: Optional[torch.Tensor] = None) -> None:
     """Rows of ``proj`` = q heads | k heads | v heads | anything: queries and keys divided per head by
     their root mean square (``eps`` None: left as they are; gains optional), queries to ``q_out``,
     keys and values of every row into their planes of the paged cache (``store``).  Keys have width
     ``dk``, values ``dv``.  Rows with a negative slot are skipped.  ``inv_freq`` [rot_dims / 2] float32: the first
     ``rot_dims`` elements of every query and key head turn by position * inv_freq (pairs half the rotated width
     apart), after the norm.  ``q_temperature`` (coef, every): queries times 1 + coef ln(floor((pos + 1) / every) + 1).
-    ``values_are_keys``: the rows carry no values; a value is its key as projected, before the norm (dv = dk)."""
-    _cuda(proj, q_out, positions, token_slot, block_table, q_gain, k_gain, inv_freq)
+    ``values_are_keys``: the rows carry no values; a value is its key as projected, before the norm (dv = dk).
+    ``bias`` float32, one number per q | k | v column: added to the rows, in float32, before anything else."""
+    _cuda(proj, q_out, positions, token_slot, block_table, q_gain, k_gain, inv_freq, bias)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == (q_heads + kv_heads) * dk + (0 if values_are_keys else kv_heads * dv)
     if inv_freq is not None:
         assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2
     if q_gain is not None:
@@ -683,7 +718,7 @@ def qkv_unit_store(proj: torch.Tensor, q_out: torch.Tensor, positions, token_slo
         _p(token_slot), _p(block_table), block_table.shape[1] if block_table is not None else 0, page_size,
         kp, vp, stride, _p(q_out), _dt(proj), proj.shape[0], q_heads, kv_heads, dk, dv, int(store),
         _p(inv_freq), int(rot_dims if inv_freq is not None else 0), float(coef), int(every), int(values_are_keys),
-        _stream()), "qkv_unit_store")
+        _p(bias), _stream()), "qkv_unit_store")
 
 
 def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, positions, token_slot,
@@ -691,14 +726,15 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
                      out: torch.Tensor, softcap: float = 0.0, chunk: int = 0, window: int = 0,
                      sink: bool = False, slopes: Optional[torch.Tensor] = None,
                      gate: Optional[torch.Tensor] = None, ctx=None, sink_logits: Optional[torch.Tensor] = None,
-                     values_in_keys: bool = False, distance_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     values_in_keys: bool = False, distance_bias: Optional[torch.Tensor] = None,
+                     gate_per_head: bool = False) -> torch.Tensor:
     """Attention of every row of ``q`` [T, q_heads * dk] over the keys of its own request, with the
     score s = (q . k) * scale changed in this order by whatever is given: ``softcap`` (s <- cap *
     tanh(s / cap)), ``slopes`` [q_heads] float32 (s <- s - slope * (pos - key pos)); keys j <= pos from
     the row's own ``chunk`` of positions and from its ``window``; ``sink``: one is added to the softmax's
     denominator, or exp(sink_logits[head]) with ``sink_logits`` [q_heads] float32 (a learned score that is
-    neither scaled nor capped).  ``gate`` (a view [T, q_heads * dv] whose rows may be strided): out *=
-    sigmoid(gate).  ``values_in_keys``: a value is the first ``dv`` elements of its key's row (``v_plane`` is
+    neither scaled nor capped).  ``gate`` (a view [T, q_heads * dv], or with ``gate_per_head`` [T, q_heads],
+    whose rows may be strided): out *= sigmoid(gate).  ``values_in_keys``: a value is the first ``dv`` elements of its key's row (``v_plane`` is
     not looked at), as in attention over compressed vectors that are key and, in part, value at once.
     ``distance_bias`` [q_heads, L] float32: entry [h, min(pos - key pos, L - 1)] is added to the score after
     everything else (a learned bias by distance; it is not scaled)."""
@@ -720,13 +756,14 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
         assert sink and sink_logits.dtype == torch.float32 and sink_logits.numel() == q_heads
     gate_stride = 0
     if gate is not None:
-        assert gate.dtype == q.dtype and gate.stride(1) == 1 and tuple(gate.shape) == tuple(out.shape)
+        assert gate.dtype == q.dtype and gate.stride(1) == 1
+        assert tuple(gate.shape) == ((tokens, q_heads) if gate_per_head else tuple(out.shape))
         gate_stride = gate.stride(0)
     if slopes is not None:
         assert slopes.dtype == torch.float32 and slopes.numel() == q_heads
     gate_ptr = None if gate is None else gate.data_ptr()
     mods = (float(scale), float(softcap or 0.0), int(chunk or 0), int(window or 0), int(bool(sink)), _p(slopes),
-            _p(sink_logits), _p(distance_bias), dist_len, v_row, gate_ptr, gate_stride)
+            _p(sink_logits), _p(distance_bias), dist_len, v_row, gate_ptr, gate_stride, int(gate_per_head))
     consts = mods + (_p(out), _stream())
     # the plain score, or one changed only by a table of biases and a learned sink, at width 128 on both
     # sides: prompt portions go to the tcgen05 kernel of the plain cache, which reads the two planes
@@ -734,7 +771,7 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
         and slopes is None and gate is None and (sink_logits is not None or not sink) \
         and page_size % 16 == 0 and stride % 128 == 0 and q_heads <= 65535
     if BIASED_FAST and ctx is not None and ctx.pf_tiles is not None and ctx.tokens == tokens \
-            and q.dtype == torch.bfloat16 and gate_stride % 2 == 0 and v_row % 8 == 0 \
+            and q.dtype == torch.bfloat16 and (gate_stride % 2 == 0 or gate_per_head) and v_row % 8 == 0 \
             and lib().tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv):
         # one-token rows: keys read once per group of query heads; longer portions: tensor-core tiles
         if ctx.n_dec:
@@ -773,12 +810,12 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
         _p(q), kp, vp, stride, _p(positions), _p(token_slot), _p(block_table), block_table.shape[1], page_size,
         _dt(q), tokens, q_heads, kv_heads, dk, dv, float(scale), float(softcap or 0.0), int(chunk or 0),
         int(window or 0), int(bool(sink)), _p(slopes), _p(sink_logits), _p(distance_bias), dist_len, v_row,
-        None if gate is None else gate.data_ptr(), gate_stride, _p(out), _stream()), "attention_biased")
+        None if gate is None else gate.data_ptr(), gate_stride, int(gate_per_head), _p(out), _stream()), "attention_biased")
     return out
 
 
 # --------------------------------------------------------------------------- stream, embedding with positions, activations
-ELEMENTWISE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2}      # codes of csrc/common.cuh (GateAct)
+ELEMENTWISE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 3}      # codes of csrc/common.cuh (GateAct); relu2 = max(x, 0)^2
 
 
 def embedding_norm(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
@@ -981,51 +1018,107 @@ def linear_recurrence(proj: torch.Tensor, kind: str, z: torch.Tensor, z_bias: to
                          out_dtype, None, 0, 1, state, den, gate_act)
 
 
+# --------------------------------------------------------------------------- selective state space
+def state_space_state_floats(heads: int, groups: int, state: int, head_dim: int, taps: int) -> int:
+    """Float32 words of one request's state of ``state_space``: S [state, head_dim] of every head in the scan
+    kernel's layout, then the convolution's last ``taps - 1`` inputs over the channels x | B | C."""
+    return delta_rule_state_floats(heads, groups, state, head_dim, 1) + (taps - 1) * (heads * head_dim + 2 * groups * state)
+
+
+def state_space(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], taps: int,
+                dt_bias: torch.Tensor, rate: torch.Tensor, skip: torch.Tensor, out_weight: torch.Tensor, eps: float,
+                norm_groups: int, token_slot: torch.Tensor, seg_info: Optional[torch.Tensor], state: torch.Tensor,
+                heads: int, groups: int, n_state: int, head_dim: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """One step of a selective state space with a decay per head, for every row of ``proj`` [T, >= 2 heads P + 2 G N
+    + heads] = z | x | B | C | dt in the storage type (P = ``head_dim``, N = ``n_state``, G = ``groups``): the causal
+    convolution ``conv_w`` [channels, taps] with bias ``conv_b`` over x | B | C and SiLU, dt = softplus(dt +
+    ``dt_bias``), per head S <- exp(-rate_h dt) S + B (dt x)^T from ``state[slot]`` (float32, updated in place), y =
+    S^T C + skip_h x, then y silu(z), an RMS norm over each of ``norm_groups`` equal parts of the row and
+    ``out_weight``.  ``dt_bias``, ``rate``, ``skip`` [heads], ``conv_b`` and ``out_weight`` are float32.  ``seg_info``
+    as in ``delta_rule``.  Returns [T, heads P] in ``out_dtype``."""
+    _cuda(proj, conv_w, conv_b, dt_bias, rate, skip, out_weight, token_slot, seg_info, state)
+    tokens, ld = proj.shape
+    inner, gn = heads * head_dim, groups * n_state
+    channels = inner + 2 * gn
+    assert dt_bias.dtype == rate.dtype == skip.dtype == out_weight.dtype == state.dtype == torch.float32
+    assert conv_w.dtype == proj.dtype and tuple(conv_w.shape) == (channels, taps) and state.dim() == 2
+    assert conv_b is None or (conv_b.dtype == torch.float32 and conv_b.numel() == channels)
+    assert out_dtype == proj.dtype and state.shape[1] == state_space_state_floats(heads, groups, n_state, head_dim, taps)
+    tail_off = delta_rule_state_floats(heads, groups, n_state, head_dim, 1)
+    ws = workspace(proj.device, tokens * (2 * gn + 3 * inner + heads * n_state) + 32)
+    at = 0
+
+    def take(n):
+        nonlocal at
+        t = ws[at:at + tokens * n]
+        at += -(-tokens * n // 4) * 4
+        return t
+    qn, kn, decay, vv, o_raw, skipped = take(gn), take(gn), take(heads * n_state), take(inner), take(inner), take(inner)
+    _check(lib().tllm_ssd_prepare(_p(proj), ld, _dt(proj), _p(conv_w), _p(conv_b), taps, _p(dt_bias), _p(rate), _p(skip),
+                                  _p(token_slot), _p(state), state.stride(0), tail_off, heads, groups, n_state, head_dim,
+                                  _p(qn), _p(kn), _p(vv), _p(decay), _p(skipped), tokens, _stream()), "ssd_prepare")
+    segments = tokens if seg_info is None else seg_info.shape[0]
+    _check(lib().tllm_delta_scan(_p(seg_info), segments, _p(token_slot), _p(qn), _p(kn), _p(vv), _p(decay), None,
+                                 _p(state), state.stride(0), heads, groups, n_state, head_dim, _p(o_raw), SCAN_PLAIN,
+                                 None, 0, 0.0, None, _stream()), "delta_scan")
+    out = torch.empty((tokens, inner), dtype=out_dtype, device=proj.device)
+    _check(lib().tllm_ssd_finish(_p(o_raw), _p(skipped), _p(proj), ld, _dt(proj), _p(out_weight), float(eps),
+                                 int(norm_groups), _p(token_slot), tokens, inner, channels, taps, _p(state),
+                                 state.stride(0), tail_off, _p(out), _stream()), "ssd_finish")
+    return out
+
+
 # --------------------------------------------------------------------------- attention over compressed vectors
 def latent_norm_store(proj: torch.Tensor, q_rank: int, rank: int, rot: int, rot_dims: int, q_gain, c_gain,
                       eps: float, freq: torch.Tensor, mag: float, positions, token_slot, block_table,
-                      plane: torch.Tensor, page_size: int, store: bool = True) -> Optional[torch.Tensor]:
-    """Rows of ``proj`` = query latent (q_rank) | key/value latent (rank) | shared key part (rot) | anything.
+                      plane: torch.Tensor, page_size: int, store: bool = True,
+                      half_pairs: bool = False) -> Optional[torch.Tensor]:
+    """Rows of ``proj`` (a view whose rows may be strided) = query latent (q_rank) | key/value latent (rank) |
+    shared key part (rot) | anything.  ``half_pairs``: the rotation pairs element i with i + rot_dims / 2 instead of
+    its neighbour.
     Returns the query latent divided by its root mean square times ``q_gain`` (None if q_rank is 0) and
     writes [normed latent times ``c_gain`` | rotated key part] of every row into its place of ``plane``
     ([pages, 1, page, rank + rot]).  Gains and ``freq`` [rot_dims / 2] are float32."""
-    _cuda(proj, q_gain, c_gain, freq, positions, token_slot, block_table)
+    _cuda(q_gain, c_gain, freq, positions, token_slot, block_table)
+    assert proj.is_cuda and proj.stride(1) == 1
     tokens = proj.shape[0]
     cq = torch.empty((tokens, q_rank), dtype=proj.dtype, device=proj.device) if q_rank else None
     pp, stride = _plane(plane)
     assert plane.dtype == proj.dtype and tuple(plane.shape[1:]) == (1, page_size, rank + rot)
-    _check(lib().tllm_latent_norm_store(_p(proj), proj.shape[1], _dt(proj), q_rank, rank, rot, rot_dims, _p(q_gain),
+    _check(lib().tllm_latent_norm_store(proj.data_ptr(), proj.stride(0), _dt(proj), q_rank, rank, rot, rot_dims, _p(q_gain),
                                         _p(c_gain), float(eps), _p(freq), float(mag), _p(positions), _p(token_slot),
                                         _p(block_table), block_table.shape[1], page_size, pp, stride, _p(cq), int(store),
-                                        tokens, _stream()), "latent_norm_store")
+                                        tokens, int(half_pairs), _stream()), "latent_norm_store")
     return cq
 
 
 def latent_query(q: torch.Tensor, lat: torch.Tensor, heads: int, plain: int, rot: int, rot_dims: int, rank: int,
-                 freq: torch.Tensor, mag: float, positions, token_slot) -> torch.Tensor:
+                 freq: torch.Tensor, mag: float, positions, token_slot, half_pairs: bool = False) -> torch.Tensor:
     """[T, heads, rank + rot]: per head ``lat`` [heads, T, rank] followed by the rotated last ``rot`` elements
-    of the head's query in ``q`` [T, heads * (plain + rot)]."""
-    _cuda(q, lat, freq, positions, token_slot)
+    of the head's query in ``q`` [T, heads * (plain + rot)] (a view whose rows may be strided)."""
+    _cuda(lat, freq, positions, token_slot)
+    assert q.is_cuda and q.stride(1) == 1
     tokens = q.shape[0]
     assert tuple(lat.shape) == (heads, tokens, rank) and lat.dtype == q.dtype and q.shape[1] == heads * (plain + rot)
     out = torch.empty((tokens, heads * (rank + rot)), dtype=q.dtype, device=q.device)
-    _check(lib().tllm_latent_query(_p(q), _p(lat), _dt(q), heads, plain, rot, rot_dims, rank, _p(freq), float(mag),
-                                   _p(positions), _p(token_slot), tokens, _p(out), _stream()), "latent_query")
+    _check(lib().tllm_latent_query(q.data_ptr(), q.stride(0), _p(lat), _dt(q), heads, plain, rot, rot_dims, rank, _p(freq), float(mag),
+                                   _p(positions), _p(token_slot), tokens, _p(out), int(half_pairs), _stream()), "latent_query")
     return out
 
 
-def heads_gate(x: torch.Tensor, gate: Optional[torch.Tensor], token_slot=None) -> torch.Tensor:
+def heads_gate(x: torch.Tensor, gate: Optional[torch.Tensor], token_slot=None, per_head: bool = False) -> torch.Tensor:
     """[T, heads * width] = x[h, t, :] * sigmoid(gate[t, h * width + :]) for ``x`` [heads, T, width]; ``gate`` is a
-    view whose rows may be strided (None: no gate)."""
+    view whose rows may be strided (None: no gate); with ``per_head`` it is [T, heads], one number per head."""
     _cuda(x, token_slot)
     heads, tokens, width = x.shape
     out = torch.empty((tokens, heads * width), dtype=x.dtype, device=x.device)
     ldg = 0
     if gate is not None:
-        assert gate.dtype == x.dtype and gate.stride(1) == 1 and tuple(gate.shape) == (tokens, heads * width)
+        assert gate.dtype == x.dtype and gate.stride(1) == 1
+        assert tuple(gate.shape) == (tokens, heads if per_head else heads * width)
         ldg = gate.stride(0)
     _check(lib().tllm_heads_gate(_p(x), None if gate is None else gate.data_ptr(), ldg, _dt(x), heads, width, tokens,
-                                 _p(token_slot), _p(out), _stream()), "heads_gate")
+                                 _p(token_slot), _p(out), int(per_head), _stream()), "heads_gate")
     return out
 
 
@@ -1047,13 +1140,34 @@ def moe_route(z: torch.Tensor, top: int, softmax_weights: bool = False):
     return ids, weights
 
 
+ROUTER_SCORES = {"sigmoid": 0, "softmax": 1}      # scores over all experts (csrc/moe.cu, moe_route_grouped)
+
+
+def moe_route_grouped(z: torch.Tensor, top: int, scores: str = "softmax", correction: Optional[torch.Tensor] = None,
+                      groups: int = 1, keep: int = 1):
+    """(ids [T, top] int32, weights [T, top] float32) from float32 router logits ``z`` [T, E]: scores s over all E
+    experts (``softmax`` or ``sigmoid``); the choice goes by s + ``correction`` ([E] float32, if given), within the
+    ``keep`` of ``groups`` equal groups of neighbouring experts whose best member scores highest; the weights are
+    the chosen experts' s as they are.  Lowest index first on ties."""
+    _cuda(z, correction)
+    assert z.dtype == torch.float32 and (correction is None or (correction.dtype == torch.float32 and correction.numel() == z.shape[1]))
+    tokens, experts = z.shape
+    ids = torch.empty((tokens, top), dtype=torch.int32, device=z.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=z.device)
+    _check(lib().tllm_moe_route_grouped(_p(z), tokens, experts, top, ROUTER_SCORES[scores], _p(correction), int(groups),
+                                        int(keep), _p(ids), _p(weights), _stream()), "moe_route_grouped")
+    return ids, weights
+
+
 class MoePlan:
     """Device-side lists that sort a step's (token, choice) assignments by expert, with the rows cut
-    into tiles of ``tile_rows`` per expert."""
+    into tiles of ``tile_rows`` per expert.  ``real``: experts that have matrices; assignments to later ones
+    (identity experts) get rows and no tiles."""
 
-    def __init__(self, ids: torch.Tensor, experts: int, tile_rows: Optional[int] = None):
+    def __init__(self, ids: torch.Tensor, experts: int, tile_rows: Optional[int] = None, real: Optional[int] = None):
         n = ids.numel()
         self.n, self.experts = n, experts
+        self.real = experts if real is None else int(real)
         self.tile_rows = tile_rows or moe_tile_rows()
         self.max_tiles = n // self.tile_rows + experts
         ints = torch.empty(experts + 2 + 3 * n + 2 * self.max_tiles, dtype=torch.int32, device=ids.device)
@@ -1067,7 +1181,7 @@ class MoePlan:
         self.offsets, self.n_tiles = take(experts + 1), take(1)
         self.row_of, self.src_of, self.expert_of_row = take(n), take(n), take(n)
         self.tile_expert, self.tile_row0 = take(self.max_tiles), take(self.max_tiles)
-        _check(lib().tllm_moe_plan(_p(ids), n, experts, self.tile_rows, _p(self.offsets), _p(self.n_tiles),
+        _check(lib().tllm_moe_plan(_p(ids), n, experts, self.real, self.tile_rows, _p(self.offsets), _p(self.n_tiles),
                                    _p(self.row_of), _p(self.src_of), _p(self.expert_of_row), _p(self.tile_expert),
                                    _p(self.tile_row0), _stream()), "moe_plan")
 
@@ -1085,15 +1199,18 @@ def moe_tcgen05_pays(rows: int, experts: int, n: int, k: int, dtype) -> bool:
 
 def moe_grouped(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, top: int, gated: bool, gather: bool,
                 weights: Optional[torch.Tensor] = None, act: str = "silu", interleaved: bool = False,
-                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                out_dtype: Optional[torch.dtype] = None, unary: bool = False) -> torch.Tensor:
     """Per row r of the plan, A[r] . W[expert of r]^T.  ``w`` is [E, N (or 2 N: gate rows, then up rows, or
     ``interleaved`` by eight), K].  ``gather``: ``a`` is [tokens, K] and a row reads its token, times ``weights``
     [tokens, top] if given.  ``gated``: the result is act(gate) * up [rows, N] in the storage type, else
-    [rows, N] float32.  A plan cut into tiles of 128 rows goes to the grouped tcgen05 product (bfloat16 in and
-    out; the gathered rows are laid out by a kernel of their own first)."""
+    [rows, N] float32, or with ``unary`` act(.) [rows, N] in the storage type (``act`` then one of
+    ``ELEMENTWISE_ACTIVATIONS``).  A plan cut into tiles of 128 rows goes to the grouped tcgen05 product (bfloat16
+    in and out; the gathered rows are laid out by a kernel of their own first).  Rows of experts without matrices
+    (``plan.real``) are left unwritten."""
     _cuda(a, w, weights)
     experts, n_total, k = w.shape
-    assert a.shape[1] == k and a.dtype == w.dtype and experts == plan.experts
+    assert a.shape[1] == k and a.dtype == w.dtype and experts == plan.real and not (gated and unary)
+    act_code = ELEMENTWISE_ACTIVATIONS[act] if unary else ACTIVATIONS[act]
     n = n_total // 2 if gated else n_total
     if plan.tile_rows == MOE_TCGEN05_TILE:
         assert a.dtype == torch.bfloat16 and (interleaved or not gated)
@@ -1105,29 +1222,34 @@ def moe_grouped(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, top: int, gated
         out = torch.empty((plan.n, n), dtype=torch.bfloat16, device=a.device)
         global tcgen05_calls
         tcgen05_calls += 1
-        flags = (1 | 4 | (ACTIVATIONS[act] << 8)) if gated else 0
+        flags = (1 | 4 | (act_code << 8)) if gated else ((16 | (act_code << 8)) if unary else 0)
         _check(lib().tllm_gemm_tcgen05_grouped(
             _p(a), _p(w), _p(out), plan.n, n_total, k, experts, flags, _p(plan.tile_expert), _p(plan.tile_row0),
             _p(plan.n_tiles), _p(plan.offsets), plan.max_tiles, _p(error_word(a.device)), _stream()),
             "gemm_tcgen05_grouped")
         return out
-    out = torch.empty((plan.n, n), dtype=a.dtype if gated else torch.float32, device=a.device)
+    out = torch.empty((plan.n, n), dtype=a.dtype if (gated or unary) else torch.float32, device=a.device)
     _check(lib().tllm_moe_grouped(
         _p(a), a.stride(0), _p(plan.src_of), _p(weights), top, _p(w), w.stride(0), _p(plan.tile_expert),
         _p(plan.tile_row0), _p(plan.n_tiles), _p(plan.offsets), _p(plan.expert_of_row), plan.n, plan.max_tiles,
-        n, k, _dt(a), int(gated), int(gather), ACTIVATIONS[act], int(interleaved), _p(out), _stream()), "moe_grouped")
+        n, k, _dt(a), 1 if gated else (2 if unary else 0), int(gather), act_code, int(interleaved), plan.real, _p(out),
+        _stream()), "moe_grouped")
     return out
 
 
 def moe_combine(y: torch.Tensor, plan: MoePlan, top: int, shared: Optional[torch.Tensor], dtype: torch.dtype,
-                weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+                weights: Optional[torch.Tensor] = None, identity_input: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = shared[t] + sum_k (weights[t, k] *) y[row of (t, k)], float32 sums, stored as ``dtype``;
-    ``y`` float32 or in the storage type."""
-    _cuda(y, shared, weights)
+    ``y`` float32 or in the storage type.  ``identity_input`` [T, width] (``dtype``): an assignment to an expert
+    without matrices (``plan.real`` or later) adds the token's row of it instead of a row of ``y``."""
+    _cuda(y, shared, weights, identity_input)
+    if identity_input is not None:
+        assert identity_input.dtype == dtype and tuple(identity_input.shape) == (plan.n // top, y.shape[1])
     tokens, width = plan.n // top, y.shape[1]
     out = torch.empty((tokens, width), dtype=dtype, device=y.device)
     if shared is not None:
         assert shared.dtype == dtype and tuple(shared.shape) == (tokens, width)
     _check(lib().tllm_moe_combine(_p(y), _dt(y), _p(plan.row_of), _p(weights), top, _p(shared), _p(out), _DT[dtype],
-                                  tokens, width, _stream()), "moe_combine")
+                                  tokens, width, _p(identity_input), _p(plan.expert_of_row), plan.real, _stream()),
+           "moe_combine")
     return out

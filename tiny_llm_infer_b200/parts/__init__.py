@@ -3,7 +3,7 @@ arrangements, each with its sizes and constants as parameters and none aware of 
 model it is used in.  Importing this package registers the built-in parts."""
 from . import (attention, attention_biased, block, delta_rule, embedding, feed_forward, latent_attention,  # noqa: F401
                linear_recurrence,
-               moe, norm, position)
+               moe, norm, position, state_space)
 from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, lookup, register,
                        unregister)
 from .spec import (CacheSpec, ExecEntry, LayerSpec, ModelDescription, ParamSpec, PartSpec,

@@ -16,7 +16,11 @@ softmax, with an output gate.  Every step is a parameter, so other designs can p
               chunks), and within ``window`` keys back (None: no window)
   softmax     ``sink``: one is added to the denominator (a key of score 0 that carries no value); with
               ``learned_sink`` exp(z_h) instead, z_h a learned number per head (tensor ``sink``)
-  gate        ``output_gate``: the concatenated heads are multiplied by sigmoid(Wg x), x the mixer's input
+  gate        ``output_gate``: the concatenated heads are multiplied by sigmoid(Wg x), x the mixer's input; with
+              ``gate_per_head`` Wg has one row per head and a head is multiplied by one number
+  biases      ``biases``: q, k, v and the output product have biases (tensors ``<name>`` + ``bias_suffix``), added in
+              float32 where the norm kernel reads the projections; the output's is added by the product, or, with
+              ``defer_output_bias``, left as ``deferred_bias`` for the block's sum kernel to add
 
 Keys have width ``key_dim`` and values ``value_dim``; they are two planes of the paged cache.  With a
 chunk or a window the cache keeps only the keys a later query can still see (a chunk never reaches
@@ -70,7 +74,8 @@ class BiasedAttention:
                  position: Optional[PartSpec] = None, values_are_keys: bool = False,
                  q_temperature: Optional[Tuple[float, int]] = None,
                  distance_bias: Optional[Tuple[int, float]] = None, bias_name: str = "rel",
-                 learned_sink: bool = False, sink_name: str = "sink"):
+                 learned_sink: bool = False, sink_name: str = "sink", gate_per_head: bool = False,
+                 biases: bool = False, bias_suffix: str = ".b", defer_output_bias: bool = False):
         if q_heads % kv_heads:
             raise ValueError(f"{q_heads} query heads cannot share {kv_heads} key/value heads")
         if unit_norm_eps is not None and not unit_norm_eps > 0.0:
@@ -121,6 +126,11 @@ class BiasedAttention:
             self.inv_freq, self.rot_dims = part.fused_rotary()
             if self.rot_dims > key_dim:
                 raise ValueError(f"a rotation of {self.rot_dims} elements in heads of {key_dim}")
+        self.gate_per_head, self.biases, self.bias_suffix = bool(gate_per_head), bool(biases), bias_suffix
+        self.defer_output_bias = bool(defer_output_bias) and self.biases
+        if self.gate_per_head and not self.output_gate:
+            raise ValueError("a gate per head is an output gate: give output_gate=True")
+        self.in_bias = self.out_bias = self.deferred_bias = None
         self.q_gain = self.k_gain = self.bias_table = self.sink_logits = None
         self.w_in = self.w_o = None
 
@@ -128,7 +138,8 @@ class BiasedAttention:
     @classmethod
     def param_specs(cls, hidden_size, q_heads, kv_heads, key_dim, value_dim, output_gate=False,
                     names=NAMES, qk_gains=False, gain_suffix=".norm", values_are_keys=False, distance_bias=None,
-                    bias_name="rel", learned_sink=False, sink_name="sink", **_) -> Dict[str, ParamSpec]:
+                    bias_name="rel", learned_sink=False, sink_name="sink", gate_per_head=False, biases=False,
+                    bias_suffix=".b", **_) -> Dict[str, ParamSpec]:
         q, k, v, o, g = names
         specs = {
             q: ParamSpec((q_heads * key_dim, hidden_size)),
@@ -138,7 +149,10 @@ class BiasedAttention:
         if not values_are_keys:
             specs[v] = ParamSpec((kv_heads * value_dim, hidden_size))
         if output_gate:
-            specs[g] = ParamSpec((q_heads * value_dim, hidden_size))
+            specs[g] = ParamSpec((q_heads if gate_per_head else q_heads * value_dim, hidden_size))
+        if biases:
+            for name in (q, k, o) + (() if values_are_keys else (v,)):
+                specs[name + bias_suffix] = ParamSpec((specs[name].shape[0],), "unit")
         if qk_gains:
             specs[q + gain_suffix] = ParamSpec((key_dim,), "norm")
             specs[k + gain_suffix] = ParamSpec((key_dim,), "norm")
@@ -152,8 +166,17 @@ class BiasedAttention:
         q, k, v, o, g = self.names
         parts = [t[q], t[k]] + ([] if self.values_are_keys else [t[v]]) + ([t[g]] if self.output_gate else [])
         common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+        if sum(p.shape[0] for p in parts) % 8:            # rows of the fused product stay whole 16-byte pieces
+            parts.append(torch.zeros((-sum(p.shape[0] for p in parts) % 8, self.hidden), dtype=common, device=parts[0].device))
         self.w_in = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
         self.w_o = t[o].contiguous()
+        if self.biases:
+            names = [q, k] + ([] if self.values_are_keys else [v])
+            self.in_bias = torch.cat([t[n + self.bias_suffix].to(torch.float32) for n in names]).contiguous()
+            if self.defer_output_bias:
+                self.deferred_bias = t[o + self.bias_suffix].to(torch.float32).contiguous()
+            else:
+                self.out_bias = t[o + self.bias_suffix].contiguous()
         if self.qk_gains:
             self.q_gain = t[q + self.gain_suffix].to(self.dtype).contiguous()
             self.k_gain = t[k + self.gain_suffix].to(self.dtype).contiguous()
@@ -192,15 +215,15 @@ class BiasedAttention:
                            cache.page_size, self.q_heads, self.kv_heads, self.dk, self.dv,
                            self.unit_norm_eps, q_gain=self.q_gain, k_gain=self.k_gain, store=cache.writes,
                            inv_freq=self.inv_freq, rot_dims=self.rot_dims, q_temperature=self.q_temperature,
-                           values_are_keys=self.values_are_keys)
+                           values_are_keys=self.values_are_keys, bias=self.in_bias)
         gate = None
         if self.output_gate:
             at = (self.q_heads + self.kv_heads) * self.dk + (0 if self.values_are_keys else self.kv_heads * self.dv)
-            gate = proj[:, at:at + self.q_heads * self.dv]
+            gate = proj[:, at:at + (self.q_heads if self.gate_per_head else self.q_heads * self.dv)]
         out = torch.empty((tokens, self.q_heads * self.dv), dtype=self.dtype, device=x.device)
         ops.attention_biased(q, k_plane, v_plane, ctx.positions, ctx.token_slot, cache.block_table,
                              cache.page_size, self.q_heads, self.kv_heads, self.dk, self.dv, self.scale, out,
                              softcap=self.softcap or 0.0, chunk=self.chunk or 0, window=self.window or 0,
                              sink=self.sink, slopes=self.slopes, gate=gate, ctx=ctx, sink_logits=self.sink_logits,
-                             distance_bias=self.bias_table)
-        return ops.linear(out, self.w_o, out_dtype=self.dtype)
+                             distance_bias=self.bias_table, gate_per_head=self.gate_per_head)
+        return ops.linear(out, self.w_o, out_dtype=self.dtype, bias=self.out_bias)

@@ -24,6 +24,13 @@ parts), the c_i weigh the mixers and m is the residual multiplier.  One mixer (`
 ``parallel_mixer_ffn``) or two side by side (``parallel_pair``, ``parallel_pair_ffn``, roles ``left`` and
 ``right``, each with a cache of its own).  The outputs go on as ``ScaledDeltas``: the norm kernel that follows
 multiplies, adds in float32 and norms in one pass.
+
+``postnorm_*``: the norm comes after the sum and its result is the stream: h <- norm1(alpha h + sum_i c_i mixer_i(h)),
+then, where the layer has a feed-forward, h <- norm2(alpha h + ffn(h)); the sub-layers read the stream itself.  One
+mixer (``postnorm_mixer``, ``postnorm_mixer_ffn``) or two side by side with weights c_i (``postnorm_pair``,
+``postnorm_pair_ffn``, roles ``left`` and ``right``).  Every sum with its norm is one kernel (``RMSNorm.of_sum``),
+which also leaves the stream in the storage type; it travels from block to block as a ``StreamCopy``.  A mixer
+that says ``deferred_bias`` (a bias of its output product that it has not added) gets it added in that kernel.
 """
 from __future__ import annotations
 
@@ -32,7 +39,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from .norm import NormedDelta, ScaledDeltas
+from .norm import NormedDelta, ScaledDeltas, StreamCopy
 from .registry import register
 
 
@@ -90,6 +97,8 @@ class SandwichMixerBlock(Block):
 
 def _stream(h: torch.Tensor, pending, dtype: torch.dtype) -> torch.Tensor:
     """h += pending (normed first if it is a ``NormedDelta``); the stream in the storage type."""
+    if isinstance(pending, StreamCopy):
+        return pending.x
     out = torch.empty(h.shape, dtype=dtype, device=h.device)
     if isinstance(pending, NormedDelta):
         return ops.stream_add(h, pending.delta, out, post_gain=pending.gain, post_eps=pending.eps)
@@ -164,3 +173,53 @@ def _parallel_block(name: str, mixer_roles, with_ffn: bool) -> type:
 for _roles, _name in ((("mixer",), "parallel_mixer"), (("left", "right"), "parallel_pair")):
     for _ffn in (False, True):
         _parallel_block(_name + ("_ffn" if _ffn else ""), _roles, _ffn)
+
+
+def _postnorm_block(name: str, mixer_roles, with_ffn: bool) -> type:
+    roles = {role: "mixer" for role in mixer_roles}
+    roles["norm1"] = "norm"
+    if with_ffn:
+        roles.update({"ffn": "feed_forward", "norm2": "norm"})
+
+    class PostNormBlock(Block):
+        def __init__(self, parts: Dict[str, object], alpha: float = 1.0, mixer_weights=None):
+            super().__init__(parts)
+            self.alpha = float(alpha)
+            self.mixer_weights = [1.0] * len(mixer_roles) if mixer_weights is None else [float(w) for w in mixer_weights]
+            if len(self.mixer_weights) != len(mixer_roles):
+                raise ValueError(f"{len(self.mixer_weights)} weights for {len(mixer_roles)} mixers")
+            self._bias: Optional[torch.Tensor] = None
+            self._bias_made = False
+
+        def mixer_bias(self) -> Optional[torch.Tensor]:
+            """The weighted sum of the biases that the mixers left to the norm's kernel (made once, after the load)."""
+            if not self._bias_made:
+                for mixer, w in zip(self.mixers(), self.mixer_weights):
+                    b = getattr(mixer, "deferred_bias", None)
+                    if b is not None:
+                        self._bias = b.to(torch.float32) * w if self._bias is None else self._bias + b.to(torch.float32) * w
+                if self._bias is not None:
+                    self._bias = self._bias.contiguous()
+                self._bias_made = True
+            return self._bias
+
+        def forward(self, h: torch.Tensor, pending, ctx, cache):
+            if isinstance(pending, StreamCopy):
+                x = pending.x
+            else:                                   # the first block of a model, or one behind a block of another kind
+                x = _stream(h, pending, self.norm1.dtype)
+            views = cache if isinstance(cache, (list, tuple)) else [cache]
+            deltas = [mixer.forward(x, ctx, view) for mixer, view in zip(self.mixers(), views)]
+            x = self.norm1.of_sum(h, self.alpha, deltas, self.mixer_weights, bias=self.mixer_bias())
+            if with_ffn:
+                x = self.norm2.of_sum(h, self.alpha, [self.ffn.forward(x, ctx)], [1.0])
+            return StreamCopy(x)
+
+    PostNormBlock.roles = roles
+    PostNormBlock.__name__ = PostNormBlock.__qualname__ = "".join(w.title() for w in name.split("_")) + "Block"
+    return register("block", name)(PostNormBlock)
+
+
+for _roles, _name in ((("mixer",), "postnorm_mixer"), (("left", "right"), "postnorm_pair")):
+    for _ffn in (False, True):
+        _postnorm_block(_name + ("_ffn" if _ffn else ""), _roles, _ffn)

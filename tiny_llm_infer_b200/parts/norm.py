@@ -13,6 +13,11 @@ keeps a plain gain in float32 too (a model whose other norms do, so that one ker
 A block that norms a sub-layer's output before the residual sum hands that output on as a
 ``NormedDelta`` (``wrap``): the norm that follows takes it as its ``delta`` and does the output's norm,
 the sum and its own norm in one kernel, h += g_post * d / sqrt(mean(d^2) + eps_post) in float32.
+
+A block that norms after the sum (``of_sum``) makes the norm's result the stream itself:
+h <- gain * v / sqrt(mean(v^2) + eps) with v = alpha h + sum_i c_i d_i (+ a bias), in one kernel that also leaves
+the new stream in the storage type for the next sub-layer; between such blocks the stream travels as a
+``StreamCopy`` (nothing is left to add).
 """
 from __future__ import annotations
 
@@ -33,6 +38,13 @@ class NormedDelta:
     delta: torch.Tensor
     gain: torch.Tensor
     eps: float
+
+
+@dataclass
+class StreamCopy:
+    """The stream as it stands, in the storage type: what a block that norms after its sums hands on in place of
+    an output still to be added."""
+    x: torch.Tensor
 
 
 @register("norm", "rmsnorm")
@@ -59,9 +71,17 @@ class RMSNorm:
         """``delta`` with this norm still to be applied to it, by the norm that adds it to the stream."""
         return NormedDelta(delta, self.gain, self.eps)
 
+    def of_sum(self, h: torch.Tensor, alpha: float, deltas, coefs, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """h <- norm(alpha h + sum_i coefs[i] deltas[i] (+ bias)), written back as the stream; returns it in the
+        storage type.  The gain must be float32 (``offset`` or ``float32_gain``)."""
+        out = torch.empty((h.shape[0], self.width), dtype=self.dtype, device=h.device)
+        return ops.sum_rmsnorm(h, list(deltas), list(coefs), alpha, self.gain, self.eps, out, bias=bias)
+
     def forward(self, h: torch.Tensor, delta, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=self.dtype, device=h.device)
+        if isinstance(delta, StreamCopy):
+            delta = None
         if isinstance(delta, NormedDelta):
             post = delta.gain if delta.gain.dtype == self.gain.dtype else delta.gain.to(self.gain.dtype)
             return ops.add_rmsnorm(h, delta.delta, self.gain, self.eps, out, rows, post_gain=post, post_eps=delta.eps)
@@ -98,7 +118,7 @@ class LayerNorm:
     def forward(self, h: torch.Tensor, delta, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=self.dtype, device=h.device)
-        if delta is None:
+        if delta is None or isinstance(delta, StreamCopy):
             deltas, scales = [], []
         elif isinstance(delta, ScaledDeltas):
             deltas, scales = delta.deltas, delta.scales

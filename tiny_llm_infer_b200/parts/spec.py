@@ -17,8 +17,9 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 class ParamSpec:
     """One tensor a part owns.  ``init`` is what random-weights mode fills it with:
     ``normal`` (matrices, embeddings), ``norm`` (norm gains, uniform in a range), ``norm_zero`` (gains
-    stored as their distance from one), ``unit`` (numbers of order one: rates, biases, learned scores) or
-    ``index`` (integer tables, kept as int32)."""
+    stored as their distance from one), ``unit`` (numbers of order one: rates, biases, learned scores), ``small``
+    (numbers of the order of a probability among many: corrections of router scores) or ``index`` (integer tables,
+    kept as int32)."""
     shape: Tuple[int, ...]
     init: str = "normal"
 

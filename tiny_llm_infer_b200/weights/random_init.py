@@ -76,7 +76,7 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, std: float, norm_range:
     count = math.prod(spec.shape) if spec.shape else 1
     if spec.init == "index":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
-    if spec.init not in ("norm", "norm_zero", "normal", "unit"):
+    if spec.init not in ("norm", "norm_zero", "normal", "unit", "small"):
         raise ValueError(f"{name}: unknown init {spec.init!r}")
     out = torch.empty(count, dtype=dtype, device=device)
     slab = 1 << 24                                       # elements made at a time (float64 and int64 temporaries)
@@ -89,6 +89,8 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, std: float, norm_range:
                 values = values - 1.0
         elif spec.init == "unit":                        # numbers of order one whatever the matrices' spread
             values = _normal(key, start, n, device) * 0.5   # (rates, biases and scores that enter an exponential)
+        elif spec.init == "small":                       # numbers that are added to probabilities
+            values = _normal(key, start, n, device) * 0.05
         else:
             values = _normal(key, start, n, device) * std
         out[start:start + n] = values.to(torch.float32).to(dtype)
