@@ -153,20 +153,28 @@ def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: dict):
 
 def router_margin(h, w, p, r) -> torch.Tensor:
     """Per token the smallest gap between a choice the router makes and the best one it does not (group choice
-    and expert choice alike); a token with a small margin may fall either way under rounding."""
+    and expert choice alike), relative to the two scores that meet there: rounding moves a score in proportion
+    to itself (the correction is a constant), so a gap that is small beside its scores may fall either way."""
     s = torch.softmax(h @ w[p + "router"].T, dim=-1)
     choice = s + w[p + "correction"]
     count, keep, top = r["groups"]["count"], r["groups"]["keep"], r["top"]
-    size = s.shape[1] // count
-    best = torch.sort(choice.view(-1, count, size).max(-1).values, dim=-1, descending=True).values
-    gap = best[:, keep - 1] - best[:, keep] if keep < count else torch.full((h.shape[0],), math.inf, dtype=h.dtype)
-    kept = torch.topk(choice.view(-1, count, size).max(-1).values, keep, dim=-1).indices
-    allowed = torch.zeros(h.shape[0], count, dtype=torch.bool)
-    allowed.scatter_(1, kept, True)
+    T, total = s.shape
+    size = total // count
+    gap = torch.full((T,), math.inf, dtype=h.dtype)
+    best, arg = choice.view(T, count, size).max(-1)
+    s_best = torch.gather(s.view(T, count, size), 2, arg.unsqueeze(-1)).squeeze(-1)
+    order = torch.argsort(best, dim=-1, descending=True)
+    if keep < count:
+        a, b = order[:, keep - 1:keep], order[:, keep:keep + 1]
+        gap = ((best.gather(1, a) - best.gather(1, b)) / (s_best.gather(1, a) + s_best.gather(1, b))).squeeze(1)
+    allowed = torch.zeros(T, count, dtype=torch.bool)
+    allowed.scatter_(1, order[:, :keep], True)
     masked = choice.masked_fill(~allowed.repeat_interleave(size, dim=1), float("-inf"))
-    order = torch.sort(masked, dim=-1, descending=True).values
-    if top < order.shape[1]:
-        gap = torch.minimum(gap, order[:, top - 1] - order[:, top])
+    order = torch.argsort(masked, dim=-1, descending=True)
+    if top < keep * size:
+        a, b = order[:, top - 1:top], order[:, top:top + 1]
+        rel = ((masked.gather(1, a) - masked.gather(1, b)) / (s.gather(1, a) + s.gather(1, b))).squeeze(1)
+        gap = torch.minimum(gap, rel)
     return gap
 
 
@@ -174,8 +182,10 @@ def expert(h, up, down):
     return relu_squared(h @ up.T) @ down.T
 
 
-def mixture(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -> torch.Tensor:
+def mixture(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict, gaps_out: Optional[list] = None) -> torch.Tensor:
     r = mlp["router"]
+    if gaps_out is not None:
+        gaps_out.append(router_margin(h, w, p, r))
     real = r["experts"]
     chosen, weights = route(h, w, p, r)
     out = torch.zeros_like(h)
@@ -196,8 +206,9 @@ def offset_norm(x, w, eps):
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
-            layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence."""
+            layers_out: Optional[list] = None, gaps_out: Optional[list] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence.  ``layers_out`` receives the stream after every layer,
+    ``gaps_out`` every router's margin per token (``router_margin``)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
     x = w["embed"][torch.tensor(tokens, dtype=torch.long)]
@@ -217,8 +228,28 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
             raise ValueError(layer["type"])
         x = offset_norm(alpha * x + a, w[p + "norm1"], eps)
         if layer.get("mlp") is not None:
-            x = offset_norm(alpha * x + mixture(x, w, p + "mlp.", layer["mlp"]), w[p + "norm2"], eps)
+            x = offset_norm(alpha * x + mixture(x, w, p + "mlp.", layer["mlp"], gaps_out), w[p + "norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     x = offset_norm(x, w["final.norm"], eps)
     return x @ w["embed"].T
+
+
+def decisive_tokens(cfg, w, tokens, seed, threshold=0.04, tries=400):
+    """``tokens`` with some of them drawn again until no router of the model meets a near-tie anywhere in the
+    sequence (every margin above ``threshold``).  In 16-bit arithmetic a near-tie falls either way, and the row
+    then differs by a whole expert; a comparison of logits wants prompts on which the design's answer does not
+    hang on the last bit.  Tokens before the first near-tie stay as they are (the model is causal), so the search
+    moves from left to right."""
+    g = torch.Generator().manual_seed(seed)
+    tokens = list(tokens)
+    for _ in range(tries):
+        gaps = []
+        forward(cfg, w, tokens, gaps_out=gaps)
+        if not gaps:
+            return tokens
+        close = (torch.stack(gaps).min(0).values < threshold).nonzero().flatten()
+        if close.numel() == 0:
+            return tokens
+        tokens[int(close[0])] = int(torch.randint(0, cfg["vocab"], (1,), generator=g))
+    raise RuntimeError("no sequence without near-ties found")
