@@ -235,7 +235,7 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
     return x @ w["embed"].T
 
 
-def decisive_tokens(cfg, w, tokens, seed, threshold=0.04, tries=400):
+def decisive_tokens(cfg, w, tokens, seed, threshold=0.12, tries=1000):
     """``tokens`` with some of them drawn again until no router of the model meets a near-tie anywhere in the
     sequence (every margin above ``threshold``).  In 16-bit arithmetic a near-tie falls either way, and the row
     then differs by a whole expert; a comparison of logits wants prompts on which the design's answer does not

