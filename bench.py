@@ -1138,6 +1138,275 @@ def tetodra_bench(args) -> int:
     return 0
 
 
+PEVOLORN_SIZES = {
+    # width; layers in the order latent attention, pair, pair, latent attention that borrows the first one's cache
+    # (repeated); latent attention: heads, unrotated and rotated query/key widths, value width, latent width (latent +
+    # rotated = 128, which the tensor-core attention kernels take); the pair's attention: heads, key/value heads, widths;
+    # the pair's state space: heads, head width, state, groups; the mixture: experts (the last two of the router's
+    # outputs are identity experts), top, expert and shared widths (top * expert + shared = the dense width of the others)
+    "1b": dict(width=2048, layers=8, vocab=32768, l_heads=16, l_dim=64, l_rot=32, l_vdim=64, l_rank=96, a_heads=16, a_kv=4,
+               a_dim=128, s_heads=32, s_dim=64, s_state=128, s_groups=4, taps=4, experts=30, identity=2, groups=8, keep=4,
+               top=4, expert_ff=1024, shared_ff=2048, ff=6144),
+    "8b": dict(width=4096, layers=4, vocab=32768, l_heads=32, l_dim=64, l_rot=32, l_vdim=64, l_rank=96, a_heads=32, a_kv=8,
+               a_dim=128, s_heads=64, s_dim=64, s_state=128, s_groups=8, taps=4, experts=62, identity=2, groups=8, keep=4,
+               top=4, expert_ff=2048, shared_ff=4096, ff=12288),
+}
+
+
+def _pevolorn_at(z):
+    from tiny_llm_infer_b200.config.pevolorn import (GroupedAttentionConfig, LatentConfig, MixtureConfig, PairConfig,
+                                                      PevolornConfig, PevolornLayerConfig, StateSpaceConfig)
+    moe = MixtureConfig(z["expert_ff"], z["experts"], z["top"], z["identity"], z["groups"], z["keep"], z["shared_ff"])
+
+    def latent(kv_from):
+        return PevolornLayerConfig("latent_attention", LatentConfig(
+            z["l_heads"], z["l_dim"], z["l_rot"], z["l_vdim"], z["l_rank"], (z["l_dim"] + z["l_rot"]) ** -0.5, 10000.0,
+            z["l_rot"], kv_from), moe)
+    pair = PevolornLayerConfig("parallel", PairConfig(
+        GroupedAttentionConfig(z["a_heads"], z["a_kv"], z["a_dim"], z["a_dim"], 8.0 / z["a_dim"], 30.0, 1000000.0, z["a_dim"] // 2),
+        StateSpaceConfig(z["s_heads"], z["s_dim"], z["s_state"], z["s_groups"], z["taps"], z["s_groups"]), 1.2, 1.1), moe)
+    layers = []
+    for i in range(z["layers"]):
+        layers.append([latent(None), pair, pair, latent(i - 3)][i % 4])
+    return PevolornConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, postln_alpha=3.0, layers=tuple(layers))
+
+
+def pevolorn_bench(args) -> int:
+    """``--design pevolorn``: prefill and decode throughput of the Pevolorn design at sizes that resemble a real
+    model's layers (random weights, bfloat16; layers in the order latent attention, attention beside a state space
+    twice, latent attention on the first one's cache; a mixture of experts on every layer), beside the closest
+    models the engine has at equal width, layers, feed-forward share and vocabulary, through the same step
+    function: Panolorn (capped attention, mixtures on every second layer) and Qwen3 dense.  Then the design's
+    kernels one by one beside their relatives, with their share of the measured peaks.  One JSON line."""
+    import torch
+    from tiny_llm_infer_b200 import ops
+    from tiny_llm_infer_b200.config import Qwen3Config
+    from tiny_llm_infer_b200.config.panolorn import (AttentionMixerConfig, FeedForwardConfig, PanolornConfig,
+                                                      PanolornLayerConfig)
+    from tiny_llm_infer_b200.engine.batch import StepContext
+    from tiny_llm_infer_b200.parts.registry import lookup
+    from tiny_llm_infer_b200.parts.spec import PartSpec
+
+    hx = _DesignHarness(args)
+    device, pk, clocks, windows = hx.device, hx.pk, hx.clocks, hx.windows
+    tokens_pf, batch, context, steps, warmup = hx.tokens_pf, hx.batch, hx.context, hx.steps, hx.warmup
+    timed, run_model = hx.timed, hx.run_model
+    record = {"sizes": {}}
+    for size_name in ([args.model] if args.model in PEVOLORN_SIZES else sorted(PEVOLORN_SIZES)):
+        z = PEVOLORN_SIZES[size_name]
+        L, W, H, G, D = z["layers"], z["width"], z["a_heads"], z["a_kv"], z["a_dim"]
+        vcfg = _pevolorn_at(z)
+        pz = DESIGN_SIZES[size_name]
+        pcfg = PanolornConfig(vocab=z["vocab"], width=W, embedding_scale=math.sqrt(W), norm_eps=1e-5, layers=tuple(
+            PanolornLayerConfig("attention", AttentionMixerConfig(H, G, D, D, 1.0 / math.sqrt(D), 50.0, pz["chunk"]),
+                                FeedForwardConfig("dense", z["ff"]) if i % 2 == 0 else
+                                FeedForwardConfig("moe", pz["expert_ff"], experts=pz["experts"], top=pz["top"], shared_ff=pz["shared_ff"]))
+            for i in range(L)))
+        qcfg = Qwen3Config(hidden_size=W, intermediate_size=z["ff"], num_hidden_layers=L, num_attention_heads=H,
+                           num_key_value_heads=G, head_dim=D, vocab_size=z["vocab"], max_position_embeddings=8192,
+                           tie_word_embeddings=True, layer_types=("full_attention",) * L)
+        # weights per layer kind: what a token multiplies with, and what a decode step of `batch` rows reads
+        lat_own = W * (z["l_heads"] * (z["l_dim"] + z["l_rot"]) + z["l_rank"] + z["l_rot"] + z["l_heads"]) \
+            + z["l_rank"] * z["l_heads"] * (z["l_dim"] + z["l_vdim"]) + z["l_heads"] * z["l_vdim"] * W
+        lat_borrowed = lat_own - W * (z["l_rank"] + z["l_rot"])
+        inner = z["s_heads"] * z["s_dim"]
+        pair_w = W * ((H + 2 * G) * D + H) + H * D * W + W * (2 * inner + 2 * z["s_groups"] * z["s_state"] + z["s_heads"]) + inner * W
+        total = z["experts"] + z["identity"]
+        moe_active = W * total + 2 * W * (z["top"] * z["expert_ff"] + z["shared_ff"])
+        moe_read = W * total + 2 * W * (min(z["experts"], batch * z["top"]) * z["expert_ff"] + z["shared_ff"])
+        kinds = [lat_own, pair_w, pair_w, lat_borrowed]
+        mix = sum(kinds[i % 4] for i in range(L))
+        v_params = {"active": mix + L * moe_active + z["vocab"] * W, "read": mix + L * moe_read + z["vocab"] * W}
+        _, v_kv, v_state = _model_costs(vcfg, context)
+        attn = W * (H + 2 * G) * D + H * D * W
+        gate = W * H * D
+        hit = min(pz["experts"], batch * pz["top"])
+        p_params = {"active": L * (attn + gate + 3 * W * z["ff"]) + (L // 2) * W * pz["experts"] + z["vocab"] * W,
+                    "read": L * (attn + gate) + (L - L // 2) * 3 * W * z["ff"]
+                    + (L // 2) * (3 * W * (hit * pz["expert_ff"] + pz["shared_ff"]) + W * pz["experts"]) + z["vocab"] * W}
+        q_params = L * (attn + 3 * W * z["ff"]) + z["vocab"] * W
+        kv = 2 * G * D * 2 * L
+        entry = {"config": z, "params": {}}
+        for label, cfg, params, kvb, st in (("pevolorn", vcfg, v_params, v_kv, v_state), ("panolorn", pcfg, p_params, kv, 0.0),
+                                            ("qwen3_dense", qcfg, {"active": q_params, "read": q_params}, kv, 0.0)):
+            print(f"[bench] design sizes {size_name}: {label}", file=sys.stderr, flush=True)
+            r = run_model(cfg, f"{label} {size_name}", params, kvb, st)
+            r["prefill_frac_of_measured"] = round(r["prefill_tflops"] / pk["bf16_tflops"], 4)
+            r["decode_hbm_frac_of_measured"] = round(r["decode_gbs"] / pk["hbm_gbs"], 4)
+            print(f"[bench] {r}", file=sys.stderr, flush=True)
+            entry[label] = r
+            entry["params"][label] = params
+        record["sizes"][size_name] = entry
+
+    # ---- kernels one by one at the larger sizes (L2 flushed between runs)
+    z = PEVOLORN_SIZES["8b"]
+    W, bf, T = z["width"], torch.bfloat16, tokens_pf
+    kern = {}
+
+    def hbm(nbytes, ms):
+        return {"us": round(ms * 1e3, 1), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)}
+
+    def tensor(flops, ms):
+        return {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1), "frac_tensor": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)}
+
+    # the norm of a weighted sum that becomes the stream, beside the sums with a norm of the other designs
+    h = torch.randn(T * 4, W, device=device)
+    deltas = [torch.randn(T * 4, W, device=device).to(bf) for _ in range(2)]
+    gain32, gain16 = torch.ones(W, device=device), torch.ones(W, device=device, dtype=bf)
+    bias = torch.randn(W, device=device)
+    out = torch.empty_like(deltas[0])
+    per = h.numel()
+    kern["sum_rmsnorm_2_outputs_bias"] = hbm(per * (8 + 2 * 2 + 2), timed(lambda: ops.sum_rmsnorm(h, deltas, [1.2, 1.1], 3.0, gain32, 1e-6, out, bias=bias)))
+    kern["sum_rmsnorm_1_output"] = hbm(per * (8 + 2 + 2), timed(lambda: ops.sum_rmsnorm(h, deltas[:1], [1.0], 3.0, gain32, 1e-6, out)))
+    kern["postnorm_add_rmsnorm"] = hbm(per * (8 + 2 + 2), timed(lambda: ops.add_rmsnorm(h, deltas[0], gain16, 1e-5, out, post_gain=gain16, post_eps=1e-5)))
+    kern["add_rmsnorm"] = hbm(per * (8 + 2 + 2), timed(lambda: ops.add_rmsnorm(h, deltas[0], gain16, 1e-5, out)))
+    del h, deltas, out
+
+    rows, page, ctx_len = 64, 16, context
+
+    def context_for(segs):
+        seg, tiles, dec, row = [], [], [], 0
+        for s, (slot, p0, n) in enumerate(segs):
+            seg.append([slot, row, n, p0])
+            if n == 1:
+                dec.append(row)
+            else:
+                tiles += [(s, off) for off in range(0, n, 64)]
+            row += n
+        tiles.sort(key=lambda t: (t[1] % 256 != 0, t[1] % 128 != 0))
+        pos = torch.tensor([p0 + i for _, p0, n in segs for i in range(n)], dtype=torch.int32, device=device)
+        slot = torch.tensor([sl for sl, _, n in segs for _ in range(n)], dtype=torch.int32, device=device)
+        return StepContext(tokens=row, token_ids=None, positions=pos, token_slot=slot, want_rows=None, segments=[],
+                           seg_info=torch.tensor(seg, dtype=torch.int32, device=device),
+                           dec_rows=None if len(dec) == row else torch.tensor(dec, dtype=torch.int32, device=device),
+                           n_dec=len(dec), pf_tiles=torch.tensor(tiles, dtype=torch.int32, device=device).view(-1, 2),
+                           n_tiles=len(tiles), n_tiles128=sum(1 for t in tiles if t[1] % 128 == 0),
+                           n_tiles256=sum(1 for t in tiles if t[1] % 256 == 0), max_context=ctx_len, max_segment=max(n for _, _, n in segs))
+
+    # the pair's attention (biases, rotation of half a head, unit queries and keys, cap, a gate per head) beside
+    # Panolorn's (unit queries and keys, cap, slopes, chunk, a gate per element) on the same kernels, and the
+    # latent attention (keys of 128 whose first 96 elements are the values, one key head for all query heads)
+    H, G, D = z["a_heads"], z["a_kv"], z["a_dim"]
+    n_pages = rows * ctx_len // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=device).view(rows, ctx_len // page).contiguous()
+    pool = (torch.randn(n_pages, 2 * G * page * D, device=device) * 0.5).to(bf)
+    k_plane = pool[:, :G * page * D].unflatten(1, (G, page, D))
+    v_plane = pool[:, G * page * D:].unflatten(1, (G, page, D))
+    lat_plane = pool[:, :page * D].unflatten(1, (1, page, D))
+    inv_freq = (1000000.0 ** (-torch.arange(D // 4, dtype=torch.float64) * 4 / D)).float().to(device)
+    in_bias = torch.randn((H + 2 * G) * D, device=device)
+    slopes = torch.rand(H, device=device) * 0.01
+    LH, rank = z["l_heads"], z["l_rank"]
+    for what, segs in (("prefill_2048", [(0, 0, T)]), ("decode_64_rows_ctx_2048", [(i, ctx_len - 1, 1) for i in range(rows)])):
+        ctx = context_for(segs)
+        n = ctx.tokens
+        q = torch.randn(n, H * D, device=device).to(bf)
+        o = torch.empty_like(q)
+        proj = torch.randn(n, (H + 2 * G) * D + 2 * H * D, device=device).to(bf)
+        head_gate, full_gate = proj[:, (H + 2 * G) * D:(H + 2 * G) * D + H], proj[:, (H + 2 * G) * D:(H + 2 * G) * D + H * D]
+        moved = n * ((H + 2 * G) * D * 2 + (H + 2 * G) * D * 2)
+        kern[f"qkv_store_bias_rotation_unit_{what}"] = hbm(moved, timed(lambda: ops.qkv_unit_store(
+            proj, q, ctx.positions, ctx.token_slot, table, k_plane, v_plane, page, H, G, D, D, 1e-6, inv_freq=inv_freq,
+            rot_dims=D // 2, bias=in_bias)))
+        kern[f"panolorn_qkv_store_unit_{what}"] = hbm(moved, timed(lambda: ops.qkv_unit_store(
+            proj, q, ctx.positions, ctx.token_slot, table, k_plane, v_plane, page, H, G, D, D, 1e-6)))
+        ql = torch.randn(n, LH * D, device=device).to(bf)
+        ol = torch.empty(n, LH * rank, device=device, dtype=bf)
+        runs = {"attention_cap_gate_per_head": (lambda: ops.attention_biased(
+                    q, k_plane, v_plane, ctx.positions, ctx.token_slot, table, page, H, G, D, D, 8.0 / D, o, softcap=30.0,
+                    gate=head_gate, gate_per_head=True, ctx=ctx), H, D, D, G * 2 * D),
+                "panolorn_attention_cap_slopes_gate": (lambda: ops.attention_biased(
+                    q, k_plane, v_plane, ctx.positions, ctx.token_slot, table, page, H, G, D, D, D ** -0.5, o, softcap=50.0,
+                    chunk=4096, sink=True, slopes=slopes, gate=full_gate, ctx=ctx), H, D, D, G * 2 * D),
+                "latent_attention_keys_are_values": (lambda: ops.attention_biased(
+                    ql, lat_plane, lat_plane, ctx.positions, ctx.token_slot, table, page, LH, 1, D, rank, D ** -0.5, ol,
+                    values_in_keys=True, ctx=ctx), LH, D, rank, D)}
+        for name, (fn, heads, dk, dv, row_elems) in runs.items():
+            ms = timed(fn)
+            kern[f"{name}_{what}"] = tensor(2.0 * heads * (dk + dv) * T * (T + 1) / 2, ms) if what.startswith("prefill") else \
+                hbm(rows * ctx_len * row_elems * 2, ms)
+    del pool, k_plane, v_plane, lat_plane
+
+    # the state space on the scan kernel beside Tetodra's gated linear attention at equal state: 2048 tokens of one
+    # request, and 64 one-token rows (state read and written once per row)
+    Hs, P, N, Gs, taps = z["s_heads"], z["s_dim"], z["s_state"], z["s_groups"], z["taps"]
+    inner, channels = Hs * P, Hs * P + 2 * Gs * N
+
+    def scan_record(n, ms, io, work, state_words):
+        total = io + work + (0 if n == T else 2 * rows * state_words * 4)
+        return {"us": round(ms * 1e3, 1), "tokens_per_s": round(n / ms * 1e3, 1),
+                "gflops_fp32": round(6.0 * n * Hs * N * P / ms / 1e6, 1), "gbs": round(total / ms / 1e6, 1),
+                "frac_hbm": round(total / ms / 1e6 / pk["hbm_gbs"], 3)}
+
+    for what, n, seg in (("prefill_2048", T, [[0, 0, T, 0]]), ("decode_64_rows", rows, None)):
+        slots = torch.zeros(n, dtype=torch.int32, device=device) if seg else torch.arange(n, dtype=torch.int32, device=device)
+        seg_info = torch.tensor(seg, dtype=torch.int32, device=device) if seg else None
+        words = ops.state_space_state_floats(Hs, Gs, N, P, taps)
+        state = torch.zeros(rows, words, device=device)
+        proj = torch.randn(n, (inner + channels + Hs + 7) // 8 * 8, device=device).to(bf)
+        conv_w = (torch.randn(channels, taps, device=device) * 0.5).to(bf)
+        conv_b = torch.randn(channels, device=device) * 0.1
+        dt_bias, rate, skip = torch.randn(Hs, device=device) - 2.0, torch.ones(Hs, device=device), torch.ones(Hs, device=device)
+        weight = torch.ones(inner, device=device)
+        ms = timed(lambda: ops.state_space(proj, conv_w, conv_b, taps, dt_bias, rate, skip, weight, 1e-6, Gs, slots, seg_info,
+                                           state, Hs, Gs, N, P, bf))
+        io = n * ((inner + channels + Hs) * 2 + inner * 2)
+        work = n * (2 * Gs * N + 3 * inner + Hs * N) * 4 * 2
+        kern[f"state_space_{what}"] = scan_record(n, ms, io, work, words)
+        del state
+        words = ops.linear_recurrence_state_floats("channel_decay", Hs, N, P)
+        state = torch.zeros(rows, words, device=device)
+        proj = torch.randn(n, Hs * (2 * N + 2 * P), device=device).to(bf)
+        gate = proj[:, Hs * (2 * N + P):]
+        zz, zb, w2 = torch.randn(n, Hs * N, device=device), torch.randn(Hs * N, device=device) + 3.0, torch.ones(P, device=device)
+        ms = timed(lambda: ops.linear_recurrence(proj, "channel_decay", zz, zb, 1.0 / 8, gate, "silu", w2, False, 1e-5, slots, seg_info,
+                                                 state, Hs, N, P, N ** -0.5, bf))
+        io = n * (Hs * (2 * N + 2 * P) * 2 + Hs * N * 4 + inner * 2)
+        work = n * (3 * Hs * N + 2 * inner) * 4 * 2
+        kern[f"tetodra_gated_linear_attention_{what}"] = scan_record(n, ms, io, work, words)
+        del state
+
+    # the mixture: the router over all experts beside the router by largest logits, and the whole part (plain experts
+    # with the squared ReLU, identity experts) beside Panolorn's (gated experts) at equal widths, 8 rows and 8192
+    E, I, top, eff, sff = z["experts"], z["identity"], z["top"], z["expert_ff"], z["shared_ff"]
+    zl = torch.randn(8192, E + I, device=device)
+    corr = torch.randn(E + I, device=device) * 0.01
+    kern["moe_route_grouped_8192_rows"] = {"us": round(timed(lambda: ops.moe_route_grouped(zl, top, "softmax", corr, z["groups"], z["keep"])) * 1e3, 1)}
+    kern["moe_route_8192_rows"] = {"us": round(timed(lambda: ops.moe_route(zl, top)) * 1e3, 1)}
+    cls = lookup("feed_forward", "moe")
+    ours = cls(dtype=bf, device=device, hidden_size=W, experts=E, top=top, expert_size=eff, activation="relu2",
+               router_scores="softmax_all", weight_on="output", gated=False, names=("up", "down"), correction=True,
+               groups=(z["groups"], z["keep"]), identity=I,
+               shared=PartSpec("mlp", dict(hidden_size=W, intermediate_size=sff, activation="relu2", names=("up", "down")), "shared."))
+    theirs = cls(dtype=bf, device=device, hidden_size=W, experts=E + I, top=top, expert_size=eff, activation="silu",
+                 shared=PartSpec("swiglu", dict(hidden_size=W, intermediate_size=sff, names=("gate", "up", "down")), "shared."))
+    for part in (ours, theirs):
+        specs = type(part).param_specs(**{k: v for k, v in dict(
+            hidden_size=W, experts=part.experts, top=top, expert_size=eff, shared=part.shared_spec, gated=part.gated,
+            names=part.names, correction=part.correction, identity=part.identity).items()})
+        part.load({name: (torch.randn(spec.shape, device=device) * (0.02 if len(spec.shape) == 2 else 0.01)).to(bf)
+                   for name, spec in specs.items()})
+    for n in (8, 8192):
+        x = torch.randn(n, W, device=device).to(bf)
+        for name, part, mats in (("mixture_plain_experts_identity", ours, 2), ("panolorn_mixture_gated_experts", theirs, 3)):
+            ms = timed(lambda: part.forward(x, None))
+            if n == 8:
+                hit = min(part.experts, n * top)
+                kern[f"{name}_{n}_rows"] = hbm(mats * W * (hit * eff + sff) * 2, ms)
+            else:
+                kern[f"{name}_{n}_rows"] = tensor(2.0 * n * mats * W * (top * eff + sff), ms)
+    ops.check_error_word(device)
+    record["kernels"] = kern
+    clock_record = clocks.stop(windows)
+    first = record["sizes"][sorted(record["sizes"])[0]]["pevolorn"]
+    print(json.dumps({"metric": f"decode tok/s @ batch {batch} (Pevolorn design sizes, context {context}, 1 B200)",
+                      "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "ms_per_step": first["decode_ms"], "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "design": "pevolorn", "clocks": clock_record, "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},
+                      **record}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1145,7 +1414,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--model", default="8b", choices=sorted(set(MODELS) | set(DESIGN_SIZES) | set(TETODRA_SIZES)),
+    ap.add_argument("--model", default="8b", choices=sorted(set(MODELS) | set(DESIGN_SIZES) | set(TETODRA_SIZES) | set(PEVOLORN_SIZES)),
                     help="the sizes: 8b is the benchmark configuration, 0.6b and 32b the other two the reference is quoted on")
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (named in the record) if memory or time needs it")
@@ -1158,7 +1427,7 @@ def main() -> int:
     ap.add_argument("--skip-check", action="store_true", help="leave out the logits check before the timed phases")
     ap.add_argument("--ref-all", action="store_true",
                     help="reference arm: its model_main --bench at batch 1, 8 and 64 instead of --batch alone")
-    ap.add_argument("--design", default=None, choices=["panolorn", "kaketar", "tetodra"],
+    ap.add_argument("--design", default=None, choices=["panolorn", "kaketar", "tetodra", "pevolorn"],
                     help="instead of the default workload: this design's prefill and decode throughput at sizes that "
                          "resemble a real model's layers beside Qwen3 dense at equal sizes, and its kernels one by one")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e", "mixed", "p128"],
@@ -1168,7 +1437,7 @@ def main() -> int:
         if args.gpus != 1 or args.impl != "ours":
             print("bench.py: --design runs this engine on one GPU")
             return 2
-        return {"kaketar": kaketar_bench, "tetodra": tetodra_bench}.get(args.design, design_bench)(args)
+        return {"kaketar": kaketar_bench, "tetodra": tetodra_bench, "pevolorn": pevolorn_bench}.get(args.design, design_bench)(args)
     if args.model not in MODELS:
         ap.error(f"--model {args.model} goes with --design")
     model_name, model_sizes = MODELS[args.model]
