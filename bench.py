@@ -1348,10 +1348,11 @@ def pevolorn_bench(args) -> int:
         conv_b = torch.randn(channels, device=device) * 0.1
         dt_bias, rate, skip = torch.randn(Hs, device=device) - 2.0, torch.ones(Hs, device=device), torch.ones(Hs, device=device)
         weight = torch.ones(inner, device=device)
+        conv_t = conv_w.t().contiguous()
         ms = timed(lambda: ops.state_space(proj, conv_w, conv_b, taps, dt_bias, rate, skip, weight, 1e-6, Gs, slots, seg_info,
-                                           state, Hs, Gs, N, P, bf))
+                                           state, Hs, Gs, N, P, bf, conv_t=conv_t))
         io = n * ((inner + channels + Hs) * 2 + inner * 2)
-        work = n * (2 * Gs * N + 3 * inner + Hs * N) * 4 * 2
+        work = n * (2 * Gs * N + 3 * inner + Hs) * 4 * 2
         kern[f"state_space_{what}"] = scan_record(n, ms, io, work, words)
         del state
         words = ops.linear_recurrence_state_floats("channel_decay", Hs, N, P)

@@ -269,8 +269,9 @@ struct ScanLayout {
 // (`beta` the write's, `fgate` the keep's) and are held under a running maximum m kept per column in the request's
 // state at `aux_off`: m' = max(f + m, i), S <- exp(f + m - m') S + exp(i - m') k v^T; its last value column is the
 // normaliser (the prepare kernel feeds it ones), whose read-out leaves as max(|n . q|, exp(-m')) + floor_eps in
-// `den` while the other columns go to o_raw [., heads, dv - 1].
-enum ScanMode : int { kScanDelta = 0, kScanPlain = 1, kScanMemory = 2 };
+// `den` while the other columns go to o_raw [., heads, dv - 1].  kScanHeadDecay: kScanPlain with one decay per
+// (token, head) for all rows of S, S <- a S + k v^T; the decays come in `beta` [., heads] and `decay` is not read.
+enum ScanMode : int { kScanDelta = 0, kScanPlain = 1, kScanMemory = 2, kScanHeadDecay = 3 };
 
 template <int R, int PER, int MODE>
 __global__ void __launch_bounds__(256, 2)
@@ -320,7 +321,7 @@ delta_scan_kernel(const int* __restrict__ seg_info, const int* __restrict__ toke
                 const size_t row = (size_t)(start + c0 + tt);
                 cp_async_f32x4(k_s + at, kn + (row * kv_heads + kvh) * dk + e);
                 cp_async_f32x4(q_s + at, qn + (row * kv_heads + kvh) * dk + e);
-                if (MODE != kScanMemory) cp_async_f32x4(g_s + at, decay + (row * heads + head) * dk + e);
+                if (MODE == kScanDelta || MODE == kScanPlain) cp_async_f32x4(g_s + at, decay + (row * heads + head) * dk + e);
             }
         } else {
             for (int i = threadIdx.x; i < n * dk; i += blockDim.x) {
@@ -329,7 +330,7 @@ delta_scan_kernel(const int* __restrict__ seg_info, const int* __restrict__ toke
                 const size_t row = (size_t)(start + c0 + tt);
                 cp_async_f32(k_s + at, kn + (row * kv_heads + kvh) * dk + e, true);
                 cp_async_f32(q_s + at, qn + (row * kv_heads + kvh) * dk + e, true);
-                if (MODE != kScanMemory) cp_async_f32(g_s + at, decay + (row * heads + head) * dk + e, true);
+                if (MODE == kScanDelta || MODE == kScanPlain) cp_async_f32(g_s + at, decay + (row * heads + head) * dk + e, true);
             }
         }
         for (int i = threadIdx.x; i < n * cols; i += blockDim.x) {
@@ -395,13 +396,15 @@ delta_scan_kernel(const int* __restrict__ seg_info, const int* __restrict__ toke
                 keep2 = make_float2(keep, keep);
             } else if (MODE == kScanPlain) {
                 write = has_beta ? b_s[tt] : 1.0f;
+            } else if (MODE == kScanHeadDecay) {
+                keep2 = make_float2(b_s[tt], b_s[tt]);
             }
 #pragma unroll
             for (int il = 0; il < PER; il += 4) {
                 const float4 k4 = kr[il >> 2];
                 kk[il >> 1] = make_float2(k4.x, k4.y);
                 kk[(il >> 1) + 1] = make_float2(k4.z, k4.w);
-                if (MODE == kScanMemory) {
+                if (MODE == kScanMemory || MODE == kScanHeadDecay) {
                     S2[il >> 1] = __fmul2_rn(S2[il >> 1], keep2);
                     S2[(il >> 1) + 1] = __fmul2_rn(S2[(il >> 1) + 1], keep2);
                 } else {
@@ -749,9 +752,10 @@ int tllm_delta_scan(const int* seg_info, int segments, const int* token_slot, co
                     long long aux_off, float floor_eps, float* den, cudaStream_t stream) {
     TLLM_REQUIRE(segments >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0,
                  "delta_scan: bad sizes");
-    TLLM_REQUIRE(mode == kScanDelta || mode == kScanPlain || mode == kScanMemory, "delta_scan: unknown recurrence %d", mode);
+    TLLM_REQUIRE(mode == kScanDelta || mode == kScanPlain || mode == kScanMemory || mode == kScanHeadDecay,
+                 "delta_scan: unknown recurrence %d", mode);
     TLLM_REQUIRE(mode == kScanMemory ? (beta != nullptr && fgate != nullptr && den != nullptr && dv >= 2 && aux_off > 0)
-                                     : decay != nullptr, "delta_scan: the recurrence lacks an operand");
+                 : mode == kScanHeadDecay ? beta != nullptr : decay != nullptr, "delta_scan: the recurrence lacks an operand");
     TLLM_REQUIRE(mode != kScanDelta || beta != nullptr, "delta_scan: the delta rule needs its betas");
     TLLM_REQUIRE(heads <= 65535, "delta_scan: %d heads", heads);
     if (segments == 0) return 0;
@@ -769,11 +773,12 @@ int tllm_delta_scan(const int* seg_info, int segments, const int* token_slot, co
     const int threads = cols * r;
     TLLM_REQUIRE(col_blocks <= 65535, "delta_scan: sizes %d x %d do not fit", dk, dv);
     const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-    const int vec = dk % 4 == 0 && per % 4 == 0 && aligned(qn) && aligned(kn) && aligned(decay);
+    const int vec = dk % 4 == 0 && per % 4 == 0 && aligned(qn) && aligned(kn) && (decay == nullptr || aligned(decay));
 #define SCAN(RR, PP)                                                                                             \
     do {                                                                                                         \
         if (mode == kScanDelta) SCAN_MODE(RR, PP, kScanDelta);                                                   \
         else if (mode == kScanPlain) SCAN_MODE(RR, PP, kScanPlain);                                              \
+        else if (mode == kScanHeadDecay) SCAN_MODE(RR, PP, kScanHeadDecay);                                      \
         else SCAN_MODE(RR, PP, kScanMemory);                                                                     \
     } while (0)
 #define SCAN_MODE(RR, PP, MM)                                                                                           \

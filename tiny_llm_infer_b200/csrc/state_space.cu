@@ -7,10 +7,11 @@
 // and queries, dt x its values, and the decay is one number per head for all N rows).  Two kernels stand around
 // the scan, for prompt portions and single tokens alike:
 //
-//   ssd_prepare  one block per token: the short causal convolution (with a bias) over the channels x | B | C of the
+//   ssd_prepare  per token: the short causal convolution (with a bias) over the channels x | B | C of the
 //                fused projection (taps that reach before the portion come from the request's state) and SiLU;
-//                dt = softplus(dt + dt_bias) without a clamp; then C, B, dt x, the decays and D x in float32.
-//   ssd_finish   one block per token: (y + D x) silu(z), an RMS norm over each of `norm_groups` equal parts of
+//                dt = softplus(dt + dt_bias) without a clamp; then C, B, dt x, D x and the decay of every head
+//                in float32.
+//   ssd_finish   per token: (y + D x) silu(z), an RMS norm over each of `norm_groups` equal parts of
 //                the row, a weight; the block of a portion's last token moves the convolution's window of the
 //                request's state on.
 //
@@ -25,20 +26,51 @@ __device__ __forceinline__ float ssd_softplus(float x) {
     return x > 20.0f ? x : log1pf(expf(x));
 }
 
-template <typename T>
+// Eight elements at a time in either storage type.
+template <typename T> struct Ld8;
+template <> struct Ld8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+template <> struct Ld8<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = raw;
+    }
+};
+
+// A token's channels are dealt to gridDim.y blocks (few rows would leave the GPU idle otherwise); every block
+// makes the token's step sizes for itself.  VEC: eight channels per thread and access (the taps as [taps][channels],
+// head width, the widths of x and of B and rows of proj multiples of eight, 16-byte boundaries); else one.
+// keep [n_rows, heads] receives the decay exp(-rate_h dt) of every head, which the scan applies to all rows of S.
+template <typename T, bool VEC>
 __global__ void ssd_prepare_kernel(const T* proj, int ld, const T* __restrict__ conv_w, const float* __restrict__ conv_b,
                                    int taps, const float* __restrict__ dt_bias, const float* __restrict__ rate,
                                    const float* __restrict__ skip_d, const int* __restrict__ token_slot,
                                    const float* state, long long state_stride, long long tail_off, int heads,
-                                   int groups, int N, int P, float* qn, float* kn, float* vv, float* decay,
+                                   int groups, int N, int P, float* qn, float* kn, float* vv, float* keep,
                                    float* skip) {
-    extern __shared__ float y[];                 // [channels] after convolution and SiLU, then dt [heads]
+    extern __shared__ float dt[];                // [heads] step sizes of the token
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const int slot = token_slot[t];
     if (slot < 0) return;
     const int inner = heads * P, gn = groups * N, channels = inner + 2 * gn;
-    float* dt = y + channels;
     int back = 0;                                // rows before this one that belong to the same portion
     for (int j = 1; j < taps; ++j) {
         if (t - j >= 0 && token_slot[t - j] == slot) back = j;
@@ -46,64 +78,113 @@ __global__ void ssd_prepare_kernel(const T* proj, int ld, const T* __restrict__ 
     }
     const float* tail = state + (long long)slot * state_stride + tail_off;
     const T* row = proj + (size_t)t * ld;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        float acc = conv_b != nullptr ? conv_b[c] : 0.0f;
-        for (int j = 0; j < taps; ++j) {
-            const float w = to_f32<T>(conv_w[(size_t)c * taps + (taps - 1 - j)]);
-            float x;
-            if (j <= back) x = to_f32<T>(proj[(size_t)(t - j) * ld + inner + c]);
-            else x = tail[(size_t)(taps - 1 - (j - back)) * channels + c];
-            acc += w * x;
-        }
-        y[c] = acc / (1.0f + expf(-acc));
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+        const float d = ssd_softplus(to_f32<T>(row[2 * inner + 2 * gn + h]) + dt_bias[h]);
+        dt[h] = d;
+        if (blockIdx.y == 0) keep[(size_t)t * heads + h] = expf(-rate[h] * d);
     }
-    for (int h = threadIdx.x; h < heads; h += blockDim.x)
-        dt[h] = ssd_softplus(to_f32<T>(row[2 * inner + 2 * gn + h]) + dt_bias[h]);
     __syncthreads();
-    for (int e = threadIdx.x; e < inner; e += blockDim.x) {
-        const int h = e / P;
-        vv[(size_t)t * inner + e] = dt[h] * y[e];
-        skip[(size_t)t * inner + e] = skip_d[h] * y[e];
-    }
-    for (int e = threadIdx.x; e < gn; e += blockDim.x) {
-        kn[(size_t)t * gn + e] = y[inner + e];
-        qn[(size_t)t * gn + e] = y[inner + gn + e];
-    }
-    for (int e = threadIdx.x; e < heads * N; e += blockDim.x) {
-        const int h = e / N;
-        decay[(size_t)t * heads * N + e] = expf(-rate[h] * dt[h]);
+    constexpr int kStep = VEC ? 8 : 1;
+    const int units = channels / kStep;
+    const int u0 = (int)((long long)units * blockIdx.y / gridDim.y), u1 = (int)((long long)units * (blockIdx.y + 1) / gridDim.y);
+    for (int u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
+        const int c = u * kStep;
+        float acc[kStep];
+        if constexpr (VEC) {
+            if (conv_b != nullptr) Ld8<float>::load(conv_b + c, reinterpret_cast<float (&)[8]>(acc));
+            else for (int e = 0; e < kStep; ++e) acc[e] = 0.0f;
+            for (int j = 0; j < taps; ++j) {
+                float w[8], x[8];
+                Ld8<T>::load(conv_w + (size_t)(taps - 1 - j) * channels + c, w);      // the taps as [taps][channels]
+                if (j <= back) Ld8<T>::load(proj + (size_t)(t - j) * ld + inner + c, x);
+                else Ld8<float>::load(tail + (size_t)(taps - 1 - (j - back)) * channels + c, x);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] += w[e] * x[e];
+            }
+        } else {
+            acc[0] = conv_b != nullptr ? conv_b[c] : 0.0f;
+            for (int j = 0; j < taps; ++j) {
+                const float w = to_f32<T>(conv_w[(size_t)c * taps + (taps - 1 - j)]);
+                const float x = j <= back ? to_f32<T>(proj[(size_t)(t - j) * ld + inner + c])
+                                          : tail[(size_t)(taps - 1 - (j - back)) * channels + c];
+                acc[0] += w * x;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < kStep; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+        if (c < inner) {                         // x: the scan's values dt x, and D x for the read-out
+            const int h = c / P;
+            float a[kStep], b[kStep];
+#pragma unroll
+            for (int e = 0; e < kStep; ++e) { a[e] = dt[h] * acc[e]; b[e] = skip_d[h] * acc[e]; }
+            if constexpr (VEC) {
+                Ld8<float>::store(vv + (size_t)t * inner + c, reinterpret_cast<float (&)[8]>(a));
+                Ld8<float>::store(skip + (size_t)t * inner + c, reinterpret_cast<float (&)[8]>(b));
+            } else {
+                vv[(size_t)t * inner + c] = a[0];
+                skip[(size_t)t * inner + c] = b[0];
+            }
+        } else {
+            float* dst = c < inner + gn ? kn + (size_t)t * gn + (c - inner) : qn + (size_t)t * gn + (c - inner - gn);
+            if constexpr (VEC) Ld8<float>::store(dst, reinterpret_cast<float (&)[8]>(acc));
+            else dst[0] = acc[0];
+        }
     }
 }
 
-template <typename T>
+// A token's norm parts are dealt to gridDim.y blocks (at most one block per part), and so are the channels of
+// the convolution's window when the token is the last of its portion.
+template <typename T, bool VEC>
 __global__ void ssd_finish_kernel(const float* o_raw, const float* skip, const T* proj, int ld,
                                   const float* __restrict__ weight, float eps, int norm_groups,
                                   const int* __restrict__ token_slot, int n_rows, int inner, int channels, int taps,
                                   float* state, long long state_stride, long long tail_off, T* out) {
-    extern __shared__ float g[];                 // [inner] the gated read-out
+    extern __shared__ __align__(16) float g[];   // [part] the gated read-out of one norm part
+    __shared__ float scratch[32];
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const int slot = token_slot[t];
+    const int part = inner / norm_groups;
+    const int p0 = norm_groups * blockIdx.y / gridDim.y, p1 = norm_groups * (blockIdx.y + 1) / gridDim.y;
     if (slot < 0) {
-        for (int e = threadIdx.x; e < inner; e += blockDim.x) out[(size_t)t * inner + e] = from_f32<T>(0.0f);
+        for (int e = p0 * part + threadIdx.x; e < p1 * part; e += blockDim.x) out[(size_t)t * inner + e] = from_f32<T>(0.0f);
         return;
     }
     const T* row = proj + (size_t)t * ld;
-    for (int e = threadIdx.x; e < inner; e += blockDim.x) {
-        const float z = to_f32<T>(row[e]);
-        g[e] = (o_raw[(size_t)t * inner + e] + skip[(size_t)t * inner + e]) * (z / (1.0f + expf(-z)));
-    }
-    __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int part = inner / norm_groups;
-    for (int p = warp; p < norm_groups; p += warps) {
-        const float* src = g + (size_t)p * part;
+    constexpr int kStep = VEC ? 8 : 1;
+    for (int p = p0; p < p1; ++p) {
+        const size_t base = (size_t)t * inner + (size_t)p * part;
         float sum = 0.0f;
-        for (int e = lane; e < part; e += 32) sum += src[e] * src[e];
-        sum = warp_sum(sum);
+        for (int e = threadIdx.x * kStep; e < part; e += blockDim.x * kStep) {
+            float o[kStep], sk[kStep], z[kStep];
+            if constexpr (VEC) {
+                Ld8<float>::load(o_raw + base + e, reinterpret_cast<float (&)[8]>(o));
+                Ld8<float>::load(skip + base + e, reinterpret_cast<float (&)[8]>(sk));
+                Ld8<T>::load(row + (size_t)p * part + e, reinterpret_cast<float (&)[8]>(z));
+            } else {
+                o[0] = o_raw[base + e]; sk[0] = skip[base + e]; z[0] = to_f32<T>(row[(size_t)p * part + e]);
+            }
+#pragma unroll
+            for (int i = 0; i < kStep; ++i) {
+                const float v = (o[i] + sk[i]) * (z[i] / (1.0f + expf(-z[i])));
+                g[e + i] = v;
+                sum += v * v;
+            }
+        }
+        sum = block_sum(sum, scratch);           // (its barriers also order the writes of g before the reads below)
         const float sc = 1.0f / sqrtf(sum / (float)part + eps);
-        for (int e = lane; e < part; e += 32)
-            out[(size_t)t * inner + (size_t)p * part + e] = from_f32<T>(src[e] * sc * weight[(size_t)p * part + e]);
+        for (int e = threadIdx.x * kStep; e < part; e += blockDim.x * kStep) {
+            if constexpr (VEC) {
+                float w[8], v[8];
+                Ld8<float>::load(weight + (size_t)p * part + e, w);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = g[e + i] * sc * w[i];
+                Ld8<T>::store(out + base + e, v);
+            } else {
+                out[base + e] = from_f32<T>(g[e] * sc * weight[(size_t)p * part + e]);
+            }
+        }
+        __syncthreads();                         // g is written again for the next part
     }
     // the portion's last row moves the convolution's window on: its taps - 1 newest inputs
     if (taps > 1 && (t + 1 >= n_rows || token_slot[t + 1] != slot)) {
@@ -111,7 +192,8 @@ __global__ void ssd_finish_kernel(const float* o_raw, const float* skip, const T
         while (len < taps - 1 && t - len >= 0 && token_slot[t - len] == slot) ++len;
         float* tail = state + (long long)slot * state_stride + tail_off;
         const int keep = taps - 1;
-        for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        const int c0 = (int)((long long)channels * blockIdx.y / gridDim.y), c1 = (int)((long long)channels * (blockIdx.y + 1) / gridDim.y);
+        for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
             for (int i = 0; i < keep; ++i) {         // ascending: an old entry is read before its place is written
                 const int from_end = keep - i;       // this entry is the from_end-th newest input
                 float x;
@@ -123,17 +205,25 @@ __global__ void ssd_finish_kernel(const float* o_raw, const float* skip, const T
     }
 }
 
+// Blocks that share a token when the tokens alone would leave the GPU idle.
+static int token_split(int rows, int most) {
+    const int sms = sm_count_cached() > 0 ? sm_count_cached() : 148;
+    int split = 1;
+    while (split * 2 <= most && (long long)rows * split < 2LL * sms) split *= 2;
+    return split;
+}
+
 }  // namespace tllm
 
 using namespace tllm;
 
 extern "C" {
 
-// conv_w [channels, taps] in the storage type, conv_b [channels] float32 or null; dt_bias, rate (the positive
-// decay rate per head) and skip_d [heads] float32.  tail_off: floats of S before the convolution's window in
-// a request's state.  Outputs float32: qn (C) and kn (B) [n_rows, groups N], vv (dt x) and skip (D x) [n_rows,
-// heads P], decay [n_rows, heads N].
-int tllm_ssd_prepare(const void* proj, int ld, int dtype, const void* conv_w, const float* conv_b, int taps,
+// conv_w [channels, taps] in the storage type and conv_t, the same taps as [taps, channels] (null: one channel
+// per thread), conv_b [channels] float32 or null; dt_bias, rate (the positive decay rate per head) and skip_d
+// [heads] float32.  tail_off: floats of S before the convolution's window in a request's state.  Outputs
+// float32: qn (C) and kn (B) [n_rows, groups N], vv (dt x) and skip (D x) [n_rows, heads P], decay [n_rows, heads].
+int tllm_ssd_prepare(const void* proj, int ld, int dtype, const void* conv_w, const void* conv_t, const float* conv_b, int taps,
                      const float* dt_bias, const float* rate, const float* skip_d, const int* token_slot,
                      const float* state, long long state_stride, long long tail_off, int heads, int groups, int N,
                      int P, float* qn, float* kn, float* vv, float* decay, float* skip, int n_rows,
@@ -144,20 +234,19 @@ int tllm_ssd_prepare(const void* proj, int ld, int dtype, const void* conv_w, co
     TLLM_REQUIRE(ld >= inner + channels + heads, "ssd_prepare: rows of %d are too short", ld);
     TLLM_REQUIRE(taps == 1 || state != nullptr, "ssd_prepare: no state for the convolution's window");
     if (n_rows == 0) return 0;
-    const size_t smem = (size_t)(channels + heads) * sizeof(float);
-    TLLM_REQUIRE(smem <= 200 * 1024, "ssd_prepare: %d channels do not fit in shared memory", channels);
-#define PREP(T)                                                                                                     \
-    do {                                                                                                            \
-        if (smem > 48 * 1024) {                                                                                     \
-            cudaError_t e = cudaFuncSetAttribute(ssd_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            if (e != cudaSuccess) { set_error("ssd_prepare: %s", cudaGetErrorString(e)); return (int)e; }           \
-        }                                                                                                           \
-        launch_pdl(kPdlOther, ssd_prepare_kernel<T>, dim3(n_rows), dim3(256), smem, stream, (const T*)proj, ld,     \
-                   (const T*)conv_w, conv_b, taps, dt_bias, rate, skip_d, token_slot, state, state_stride, tail_off, \
-                   heads, groups, N, P, qn, kn, vv, decay, skip);                                                   \
-    } while (0)
-    if (dtype == kBF16) PREP(bf16);
-    else if (dtype == kF32) PREP(float);
+    const size_t smem = (size_t)heads * sizeof(float);
+    TLLM_REQUIRE(smem <= 48 * 1024, "ssd_prepare: %d heads", heads);
+    const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool vec = conv_t != nullptr && P % 8 == 0 && (groups * N) % 8 == 0 && ld % 8 == 0 && tail_off % 4 == 0 &&
+                     state_stride % 4 == 0 && al(proj) && al(conv_t) && al(conv_b) && al(state) && al(qn) && al(kn) &&
+                     al(vv) && al(skip);
+    const int split = token_split(n_rows, channels / 256 > 0 ? channels / 256 : 1);
+#define PREP(T, V)                                                                                                  \
+    launch_pdl(kPdlOther, ssd_prepare_kernel<T, V>, dim3(n_rows, split), dim3(split > 1 ? 128 : 256), smem, stream, \
+               (const T*)proj, ld, (const T*)(V ? conv_t : conv_w), conv_b, taps, dt_bias, rate, skip_d, token_slot, \
+               state, state_stride, tail_off, heads, groups, N, P, qn, kn, vv, decay, skip)
+    if (dtype == kBF16) { if (vec) PREP(bf16, true); else PREP(bf16, false); }
+    else if (dtype == kF32) { if (vec) PREP(float, true); else PREP(float, false); }
     else TLLM_REQUIRE(false, "ssd_prepare: unknown dtype %d", dtype);
 #undef PREP
     return finish_launch("ssd_prepare");
@@ -172,20 +261,24 @@ int tllm_ssd_finish(const float* o_raw, const float* skip, const void* proj, int
                  "ssd_finish: bad sizes");
     TLLM_REQUIRE(ld >= inner + channels, "ssd_finish: rows of %d are too short", ld);
     if (n_rows == 0) return 0;
-    const size_t smem = (size_t)inner * sizeof(float);
-    TLLM_REQUIRE(smem <= 200 * 1024, "ssd_finish: rows of %d do not fit in shared memory", inner);
-#define FIN(T)                                                                                                      \
+    const int part = inner / norm_groups;
+    const size_t smem = (size_t)part * sizeof(float);
+    TLLM_REQUIRE(smem <= 200 * 1024, "ssd_finish: parts of %d do not fit in shared memory", part);
+    const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool vec = part % 8 == 0 && ld % 8 == 0 && al(o_raw) && al(skip) && al(proj) && al(weight) && al(out);
+    const int split = token_split(n_rows, norm_groups);
+#define FIN(T, V)                                                                                                   \
     do {                                                                                                            \
         if (smem > 48 * 1024) {                                                                                     \
-            cudaError_t e = cudaFuncSetAttribute(ssd_finish_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(ssd_finish_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) { set_error("ssd_finish: %s", cudaGetErrorString(e)); return (int)e; }            \
         }                                                                                                           \
-        launch_pdl(kPdlOther, ssd_finish_kernel<T>, dim3(n_rows), dim3(256), smem, stream, o_raw, skip,             \
+        launch_pdl(kPdlOther, ssd_finish_kernel<T, V>, dim3(n_rows, split), dim3(256), smem, stream, o_raw, skip,   \
                    (const T*)proj, ld, weight, eps, norm_groups, token_slot, n_rows, inner, channels, taps, state,  \
                    state_stride, tail_off, (T*)out);                                                                \
     } while (0)
-    if (dtype == kBF16) FIN(bf16);
-    else if (dtype == kF32) FIN(float);
+    if (dtype == kBF16) { if (vec) FIN(bf16, true); else FIN(bf16, false); }
+    else if (dtype == kF32) { if (vec) FIN(float, true); else FIN(float, false); }
     else TLLM_REQUIRE(false, "ssd_finish: unknown dtype %d", dtype);
 #undef FIN
     return finish_launch("ssd_finish");

@@ -95,7 +95,7 @@ def _declare(h) -> None:
         "tllm_moe_gather": [vp, vp, vp, i32, vp, i32, i32, vp],
         "tllm_moe_combine": [vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, vp, vp, i32, vp],
         "tllm_sum_rmsnorm": [vp, vp, vp, i32, f32, vp, vp, f32, vp, i32, i32, i32, vp],
-        "tllm_ssd_prepare": [vp, i32, i32, vp, vp, i32, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp,
+        "tllm_ssd_prepare": [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp,
                              vp, vp, i32, vp],
         "tllm_ssd_finish": [vp, vp, vp, i32, i32, vp, f32, i32, vp, i32, i32, i32, i32, vp, i64, i64, vp, vp],
         "tllm_gemm_tcgen05_grouped": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp],
@@ -898,7 +898,7 @@ def delta_rule_state_floats(heads: int, kv_heads: int, dk: int, dv: int, taps: i
     return int(lib().tllm_delta_rule_state_floats(heads, kv_heads, dk, dv, taps))
 
 
-SCAN_DELTA, SCAN_PLAIN, SCAN_MEMORY = 0, 1, 2        # recurrences of the scan kernel (csrc/delta_rule.cu, ScanMode)
+SCAN_DELTA, SCAN_PLAIN, SCAN_MEMORY, SCAN_HEAD_DECAY = 0, 1, 2, 3     # recurrences of the scan kernel (csrc/delta_rule.cu, ScanMode)
 GATE_ACTS = {"sigmoid": 0, "silu": 1}                # what the read-out is multiplied by: act(gate)
 
 
@@ -1028,15 +1028,17 @@ def state_space_state_floats(heads: int, groups: int, state: int, head_dim: int,
 def state_space(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], taps: int,
                 dt_bias: torch.Tensor, rate: torch.Tensor, skip: torch.Tensor, out_weight: torch.Tensor, eps: float,
                 norm_groups: int, token_slot: torch.Tensor, seg_info: Optional[torch.Tensor], state: torch.Tensor,
-                heads: int, groups: int, n_state: int, head_dim: int, out_dtype: torch.dtype) -> torch.Tensor:
+                heads: int, groups: int, n_state: int, head_dim: int, out_dtype: torch.dtype,
+                conv_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One step of a selective state space with a decay per head, for every row of ``proj`` [T, >= 2 heads P + 2 G N
     + heads] = z | x | B | C | dt in the storage type (P = ``head_dim``, N = ``n_state``, G = ``groups``): the causal
     convolution ``conv_w`` [channels, taps] with bias ``conv_b`` over x | B | C and SiLU, dt = softplus(dt +
     ``dt_bias``), per head S <- exp(-rate_h dt) S + B (dt x)^T from ``state[slot]`` (float32, updated in place), y =
     S^T C + skip_h x, then y silu(z), an RMS norm over each of ``norm_groups`` equal parts of the row and
     ``out_weight``.  ``dt_bias``, ``rate``, ``skip`` [heads], ``conv_b`` and ``out_weight`` are float32.  ``seg_info``
-    as in ``delta_rule``.  Returns [T, heads P] in ``out_dtype``."""
-    _cuda(proj, conv_w, conv_b, dt_bias, rate, skip, out_weight, token_slot, seg_info, state)
+    as in ``delta_rule``.  ``conv_t``: the taps once more as [taps, channels], which lets the kernels take eight
+    channels per access.  Returns [T, heads P] in ``out_dtype``."""
+    _cuda(proj, conv_w, conv_b, dt_bias, rate, skip, out_weight, token_slot, seg_info, state, conv_t)
     tokens, ld = proj.shape
     inner, gn = heads * head_dim, groups * n_state
     channels = inner + 2 * gn
@@ -1045,7 +1047,7 @@ def state_space(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch
     assert conv_b is None or (conv_b.dtype == torch.float32 and conv_b.numel() == channels)
     assert out_dtype == proj.dtype and state.shape[1] == state_space_state_floats(heads, groups, n_state, head_dim, taps)
     tail_off = delta_rule_state_floats(heads, groups, n_state, head_dim, 1)
-    ws = workspace(proj.device, tokens * (2 * gn + 3 * inner + heads * n_state) + 32)
+    ws = workspace(proj.device, tokens * (2 * gn + 3 * inner + heads) + 32)
     at = 0
 
     def take(n):
@@ -1053,13 +1055,13 @@ def state_space(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch
         t = ws[at:at + tokens * n]
         at += -(-tokens * n // 4) * 4
         return t
-    qn, kn, decay, vv, o_raw, skipped = take(gn), take(gn), take(heads * n_state), take(inner), take(inner), take(inner)
-    _check(lib().tllm_ssd_prepare(_p(proj), ld, _dt(proj), _p(conv_w), _p(conv_b), taps, _p(dt_bias), _p(rate), _p(skip),
+    qn, kn, decay, vv, o_raw, skipped = take(gn), take(gn), take(heads), take(inner), take(inner), take(inner)
+    _check(lib().tllm_ssd_prepare(_p(proj), ld, _dt(proj), _p(conv_w), _p(conv_t), _p(conv_b), taps, _p(dt_bias), _p(rate), _p(skip),
                                   _p(token_slot), _p(state), state.stride(0), tail_off, heads, groups, n_state, head_dim,
                                   _p(qn), _p(kn), _p(vv), _p(decay), _p(skipped), tokens, _stream()), "ssd_prepare")
     segments = tokens if seg_info is None else seg_info.shape[0]
-    _check(lib().tllm_delta_scan(_p(seg_info), segments, _p(token_slot), _p(qn), _p(kn), _p(vv), _p(decay), None,
-                                 _p(state), state.stride(0), heads, groups, n_state, head_dim, _p(o_raw), SCAN_PLAIN,
+    _check(lib().tllm_delta_scan(_p(seg_info), segments, _p(token_slot), _p(qn), _p(kn), _p(vv), None, _p(decay),
+                                 _p(state), state.stride(0), heads, groups, n_state, head_dim, _p(o_raw), SCAN_HEAD_DECAY,
                                  None, 0, 0.0, None, _stream()), "delta_scan")
     out = torch.empty((tokens, inner), dtype=out_dtype, device=proj.device)
     _check(lib().tllm_ssd_finish(_p(o_raw), _p(skipped), _p(proj), ld, _dt(proj), _p(out_weight), float(eps),

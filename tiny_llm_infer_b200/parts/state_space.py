@@ -11,8 +11,8 @@ mixer.  For the row's input x, with H heads of width P (``head_dim``), a state o
 
 The state (S of every head in the scan kernel's layout, then the convolution's last taps - 1 inputs) is float32,
 zeroed at admission and carried from step to step, so a prompt may come in portions of any size.  The recurrence
-runs on the scan kernel of the delta rule in its form without a correction (keys B, queries C, values dt u, one
-decay per head for all rows); everything behind the projection is float32.  Tensors: ``in``, ``conv``,
+runs on the scan kernel of the delta rule in its form with one decay per head for all rows of S and no correction
+(keys B, queries C, values dt u); everything behind the projection is float32.  Tensors: ``in``, ``conv``,
 ``conv.b``, ``dt_bias``, ``A_log``, ``D``, ``norm``, ``o`` (``names``).
 """
 from __future__ import annotations
@@ -65,6 +65,7 @@ class StateSpace:
         pad = torch.zeros((-w.shape[0] % 8, self.hidden), dtype=w.dtype, device=w.device)
         self.w_in = torch.cat([w, pad], dim=0).contiguous()
         self.conv_w = t[conv].to(self.dtype).contiguous()
+        self.conv_t = self.conv_w.t().contiguous()                  # [taps, channels]: eight channels per access
         self.conv_b = t[conv_b].to(torch.float32).contiguous()
         self.dt_bias = t[dt_bias].to(torch.float32).contiguous()
         self.rate = torch.exp(t[a_log].to(torch.float32)).contiguous()       # the decay is exp(-rate dt)
@@ -81,8 +82,7 @@ class StateSpace:
         return StateSpec((self.heads * per * self.p + (self.taps - 1) * self.channels,), "float32")
 
     def workspace_floats(self, tokens: int) -> int:
-        return tokens * (2 * self.inner + self.channels + self.heads + 3 * self.inner + 2 * self.groups * self.n
-                         + self.heads * self.n)
+        return tokens * (2 * self.inner + self.channels + 2 * self.heads + 3 * self.inner + 2 * self.groups * self.n)
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         if not self._checked:
@@ -93,5 +93,5 @@ class StateSpace:
         proj = ops.linear(x, self.w_in, out_dtype=self.dtype)
         y = ops.state_space(proj, self.conv_w, self.conv_b, self.taps, self.dt_bias, self.rate, self.skip,
                             self.out_weight, self.norm_eps, self.norm_groups, ctx.token_slot, ctx.seg_info,
-                            cache.state, self.heads, self.groups, self.n, self.p, self.dtype)
+                            cache.state, self.heads, self.groups, self.n, self.p, self.dtype, conv_t=self.conv_t)
         return ops.linear(y, self.w_o, out_dtype=self.dtype)
