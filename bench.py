@@ -1352,7 +1352,7 @@ def pevolorn_bench(args) -> int:
         ms = timed(lambda: ops.state_space(proj, conv_w, conv_b, taps, dt_bias, rate, skip, weight, 1e-6, Gs, slots, seg_info,
                                            state, Hs, Gs, N, P, bf, conv_t=conv_t))
         io = n * ((inner + channels + Hs) * 2 + inner * 2)
-        work = n * (2 * Gs * N + 3 * inner + Hs) * 4 * 2
+        work = n * (2 * Gs * N + 2 * inner + 2 * Hs) * 4 * 2
         kern[f"state_space_{what}"] = scan_record(n, ms, io, work, words)
         del state
         words = ops.linear_recurrence_state_floats("channel_decay", Hs, N, P)

@@ -270,7 +270,8 @@ struct ScanLayout {
 // state at `aux_off`: m' = max(f + m, i), S <- exp(f + m - m') S + exp(i - m') k v^T; its last value column is the
 // normaliser (the prepare kernel feeds it ones), whose read-out leaves as max(|n . q|, exp(-m')) + floor_eps in
 // `den` while the other columns go to o_raw [., heads, dv - 1].  kScanHeadDecay: kScanPlain with one decay per
-// (token, head) for all rows of S, S <- a S + k v^T; the decays come in `beta` [., heads] and `decay` is not read.
+// (token, head) for all rows of S and a write strength likewise, S <- a S + k (w v)^T; the decays come in `beta`
+// [., heads], the strengths in `fgate` [., heads], and `decay` is not read.
 enum ScanMode : int { kScanDelta = 0, kScanPlain = 1, kScanMemory = 2, kScanHeadDecay = 3 };
 
 template <int R, int PER, int MODE>
@@ -341,7 +342,7 @@ delta_scan_kernel(const int* __restrict__ seg_info, const int* __restrict__ toke
         if (beta != nullptr)
             for (int i = threadIdx.x; i < n; i += blockDim.x)
                 cp_async_f32(b_s + i, beta + (size_t)(start + c0 + i) * heads + head, true);
-        if (MODE == kScanMemory)
+        if (MODE == kScanMemory || MODE == kScanHeadDecay)
             for (int i = threadIdx.x; i < n; i += blockDim.x)
                 cp_async_f32(f_s + i, fgate + (size_t)(start + c0 + i) * heads + head, true);
         asm volatile("cp.async.commit_group;\n" ::);
@@ -398,6 +399,7 @@ delta_scan_kernel(const int* __restrict__ seg_info, const int* __restrict__ toke
                 write = has_beta ? b_s[tt] : 1.0f;
             } else if (MODE == kScanHeadDecay) {
                 keep2 = make_float2(b_s[tt], b_s[tt]);
+                write = f_s[tt];
             }
 #pragma unroll
             for (int il = 0; il < PER; il += 4) {
@@ -755,7 +757,7 @@ int tllm_delta_scan(const int* seg_info, int segments, const int* token_slot, co
     TLLM_REQUIRE(mode == kScanDelta || mode == kScanPlain || mode == kScanMemory || mode == kScanHeadDecay,
                  "delta_scan: unknown recurrence %d", mode);
     TLLM_REQUIRE(mode == kScanMemory ? (beta != nullptr && fgate != nullptr && den != nullptr && dv >= 2 && aux_off > 0)
-                 : mode == kScanHeadDecay ? beta != nullptr : decay != nullptr, "delta_scan: the recurrence lacks an operand");
+                 : mode == kScanHeadDecay ? (beta != nullptr && fgate != nullptr) : decay != nullptr, "delta_scan: the recurrence lacks an operand");
     TLLM_REQUIRE(mode != kScanDelta || beta != nullptr, "delta_scan: the delta rule needs its betas");
     TLLM_REQUIRE(heads <= 65535, "delta_scan: %d heads", heads);
     if (segments == 0) return 0;

@@ -9,8 +9,8 @@
 //
 //   ssd_prepare  per token: the short causal convolution (with a bias) over the channels x | B | C of the
 //                fused projection (taps that reach before the portion come from the request's state) and SiLU;
-//                dt = softplus(dt + dt_bias) without a clamp; then C, B, dt x, D x and the decay of every head
-//                in float32.
+//                dt = softplus(dt + dt_bias) without a clamp; then C, B, x, and per head dt and the decay, in
+//                float32 (the scan multiplies x by dt as its write strength, the finish kernel by D).
 //   ssd_finish   per token: (y + D x) silu(z), an RMS norm over each of `norm_groups` equal parts of
 //                the row, a weight; the block of a portion's last token moves the convolution's window of the
 //                request's state on.
@@ -54,18 +54,19 @@ template <> struct Ld8<bf16> {
     }
 };
 
-// A token's channels are dealt to gridDim.y blocks (few rows would leave the GPU idle otherwise); every block
-// makes the token's step sizes for itself.  VEC: eight channels per thread and access (the taps as [taps][channels],
+// A token's channels are dealt to gridDim.y blocks (few rows would leave the GPU idle otherwise); the first
+// makes the token's step sizes.  VEC: eight channels per thread and access (the taps as [taps][channels],
 // head width, the widths of x and of B and rows of proj multiples of eight, 16-byte boundaries); else one.
-// keep [n_rows, heads] receives the decay exp(-rate_h dt) of every head, which the scan applies to all rows of S.
-template <typename T, bool VEC>
+// keep [n_rows, heads] receives the decay exp(-rate_h dt) of every head, which the scan applies to all rows of S,
+// and step [n_rows, heads] dt itself.  TAPS: the number of taps if it is 2, 3 or 4 (their loads are then all
+// issued before the first product), 0 for any other number.
+template <typename T, bool VEC, int TAPS>
 __global__ void ssd_prepare_kernel(const T* proj, int ld, const T* __restrict__ conv_w, const float* __restrict__ conv_b,
                                    int taps, const float* __restrict__ dt_bias, const float* __restrict__ rate,
-                                   const float* __restrict__ skip_d, const int* __restrict__ token_slot,
+                                   const int* __restrict__ token_slot,
                                    const float* state, long long state_stride, long long tail_off, int heads,
                                    int groups, int N, int P, float* qn, float* kn, float* vv, float* keep,
-                                   float* skip) {
-    extern __shared__ float dt[];                // [heads] step sizes of the token
+                                   float* step) {
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const int slot = token_slot[t];
@@ -78,12 +79,12 @@ __global__ void ssd_prepare_kernel(const T* proj, int ld, const T* __restrict__ 
     }
     const float* tail = state + (long long)slot * state_stride + tail_off;
     const T* row = proj + (size_t)t * ld;
-    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
-        const float d = ssd_softplus(to_f32<T>(row[2 * inner + 2 * gn + h]) + dt_bias[h]);
-        dt[h] = d;
-        if (blockIdx.y == 0) keep[(size_t)t * heads + h] = expf(-rate[h] * d);
-    }
-    __syncthreads();
+    if (blockIdx.y == 0)
+        for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+            const float d = ssd_softplus(to_f32<T>(row[2 * inner + 2 * gn + h]) + dt_bias[h]);
+            keep[(size_t)t * heads + h] = expf(-rate[h] * d);
+            step[(size_t)t * heads + h] = d;
+        }
     constexpr int kStep = VEC ? 8 : 1;
     const int units = channels / kStep;
     const int u0 = (int)((long long)units * blockIdx.y / gridDim.y), u1 = (int)((long long)units * (blockIdx.y + 1) / gridDim.y);
@@ -93,13 +94,27 @@ __global__ void ssd_prepare_kernel(const T* proj, int ld, const T* __restrict__ 
         if constexpr (VEC) {
             if (conv_b != nullptr) Ld8<float>::load(conv_b + c, reinterpret_cast<float (&)[8]>(acc));
             else for (int e = 0; e < kStep; ++e) acc[e] = 0.0f;
-            for (int j = 0; j < taps; ++j) {
-                float w[8], x[8];
-                Ld8<T>::load(conv_w + (size_t)(taps - 1 - j) * channels + c, w);      // the taps as [taps][channels]
-                if (j <= back) Ld8<T>::load(proj + (size_t)(t - j) * ld + inner + c, x);
-                else Ld8<float>::load(tail + (size_t)(taps - 1 - (j - back)) * channels + c, x);
+            if constexpr (TAPS > 0) {
+                float w[TAPS > 0 ? TAPS : 1][8], x[TAPS > 0 ? TAPS : 1][8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[e] += w[e] * x[e];
+                for (int j = 0; j < TAPS; ++j) {
+                    Ld8<T>::load(conv_w + (size_t)(TAPS - 1 - j) * channels + c, w[j]);     // the taps as [taps][channels]
+                    if (j <= back) Ld8<T>::load(proj + (size_t)(t - j) * ld + inner + c, x[j]);
+                    else Ld8<float>::load(tail + (size_t)(TAPS - 1 - (j - back)) * channels + c, x[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < TAPS; ++j)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] += w[j][e] * x[j][e];
+            } else {
+                for (int j = 0; j < taps; ++j) {
+                    float w[8], x[8];
+                    Ld8<T>::load(conv_w + (size_t)(taps - 1 - j) * channels + c, w);
+                    if (j <= back) Ld8<T>::load(proj + (size_t)(t - j) * ld + inner + c, x);
+                    else Ld8<float>::load(tail + (size_t)(taps - 1 - (j - back)) * channels + c, x);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] += w[e] * x[e];
+                }
             }
         } else {
             acc[0] = conv_b != nullptr ? conv_b[c] : 0.0f;
@@ -112,18 +127,9 @@ __global__ void ssd_prepare_kernel(const T* proj, int ld, const T* __restrict__ 
         }
 #pragma unroll
         for (int e = 0; e < kStep; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
-        if (c < inner) {                         // x: the scan's values dt x, and D x for the read-out
-            const int h = c / P;
-            float a[kStep], b[kStep];
-#pragma unroll
-            for (int e = 0; e < kStep; ++e) { a[e] = dt[h] * acc[e]; b[e] = skip_d[h] * acc[e]; }
-            if constexpr (VEC) {
-                Ld8<float>::store(vv + (size_t)t * inner + c, reinterpret_cast<float (&)[8]>(a));
-                Ld8<float>::store(skip + (size_t)t * inner + c, reinterpret_cast<float (&)[8]>(b));
-            } else {
-                vv[(size_t)t * inner + c] = a[0];
-                skip[(size_t)t * inner + c] = b[0];
-            }
+        if (c < inner) {                         // x: the scan's values (it multiplies them by dt) and the read-out's D x
+            if constexpr (VEC) Ld8<float>::store(vv + (size_t)t * inner + c, reinterpret_cast<float (&)[8]>(acc));
+            else vv[(size_t)t * inner + c] = acc[0];
         } else {
             float* dst = c < inner + gn ? kn + (size_t)t * gn + (c - inner) : qn + (size_t)t * gn + (c - inner - gn);
             if constexpr (VEC) Ld8<float>::store(dst, reinterpret_cast<float (&)[8]>(acc));
@@ -134,12 +140,15 @@ __global__ void ssd_prepare_kernel(const T* proj, int ld, const T* __restrict__ 
 
 // A token's norm parts are dealt to gridDim.y blocks (at most one block per part), and so are the channels of
 // the convolution's window when the token is the last of its portion.
+// xs [n_rows, inner]: x after convolution and SiLU; skip_d [heads]: y gets skip_d[h] * x added.  A block whose parts
+// are at least as many as its warps gives each warp parts of its own (no barrier on the way); else all threads
+// share a part.
 template <typename T, bool VEC>
-__global__ void ssd_finish_kernel(const float* o_raw, const float* skip, const T* proj, int ld,
+__global__ void ssd_finish_kernel(const float* o_raw, const float* xs, const float* __restrict__ skip_d, int P, const T* proj, int ld,
                                   const float* __restrict__ weight, float eps, int norm_groups,
                                   const int* __restrict__ token_slot, int n_rows, int inner, int channels, int taps,
                                   float* state, long long state_stride, long long tail_off, T* out) {
-    extern __shared__ __align__(16) float g[];   // [part] the gated read-out of one norm part
+    extern __shared__ __align__(16) float g[];   // the gated read-out of one norm part, per warp or for the block
     __shared__ float scratch[32];
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
@@ -152,39 +161,48 @@ __global__ void ssd_finish_kernel(const float* o_raw, const float* skip, const T
     }
     const T* row = proj + (size_t)t * ld;
     constexpr int kStep = VEC ? 8 : 1;
-    for (int p = p0; p < p1; ++p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const bool by_warp = p1 - p0 >= warps;       // the same for all threads of the block
+    // a group (a warp, or the whole block) walks one part: gated read-out into shared memory, sum, scaling
+    const int first = by_warp ? p0 + warp : p0, stride_p = by_warp ? warps : 1;
+    const int tid = by_warp ? lane : threadIdx.x, nthr = by_warp ? 32 : blockDim.x;
+    for (int p = first; p < p1; p += stride_p) {
         const size_t base = (size_t)t * inner + (size_t)p * part;
+        float* gp = g + (by_warp ? (size_t)warp * part : 0);
         float sum = 0.0f;
-        for (int e = threadIdx.x * kStep; e < part; e += blockDim.x * kStep) {
-            float o[kStep], sk[kStep], z[kStep];
+        for (int e = tid * kStep; e < part; e += nthr * kStep) {
+            float o[kStep], x[kStep], z[kStep];
             if constexpr (VEC) {
                 Ld8<float>::load(o_raw + base + e, reinterpret_cast<float (&)[8]>(o));
-                Ld8<float>::load(skip + base + e, reinterpret_cast<float (&)[8]>(sk));
+                Ld8<float>::load(xs + base + e, reinterpret_cast<float (&)[8]>(x));
                 Ld8<T>::load(row + (size_t)p * part + e, reinterpret_cast<float (&)[8]>(z));
             } else {
-                o[0] = o_raw[base + e]; sk[0] = skip[base + e]; z[0] = to_f32<T>(row[(size_t)p * part + e]);
+                o[0] = o_raw[base + e]; x[0] = xs[base + e]; z[0] = to_f32<T>(row[(size_t)p * part + e]);
             }
+            const float d = skip_d[((size_t)p * part + e) / P];       // (eight neighbours share a head in the vector form)
 #pragma unroll
             for (int i = 0; i < kStep; ++i) {
-                const float v = (o[i] + sk[i]) * (z[i] / (1.0f + expf(-z[i])));
-                g[e + i] = v;
+                const float v = (o[i] + d * x[i]) * (z[i] / (1.0f + expf(-z[i])));
+                gp[e + i] = v;
                 sum += v * v;
             }
         }
-        sum = block_sum(sum, scratch);           // (its barriers also order the writes of g before the reads below)
+        if (by_warp) { sum = warp_sum(sum); __syncwarp(); }
+        else sum = block_sum(sum, scratch);      // (its barriers also order the writes of g before the reads below)
         const float sc = 1.0f / sqrtf(sum / (float)part + eps);
-        for (int e = threadIdx.x * kStep; e < part; e += blockDim.x * kStep) {
+        for (int e = tid * kStep; e < part; e += nthr * kStep) {
             if constexpr (VEC) {
                 float w[8], v[8];
                 Ld8<float>::load(weight + (size_t)p * part + e, w);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = g[e + i] * sc * w[i];
+                for (int i = 0; i < 8; ++i) v[i] = gp[e + i] * sc * w[i];
                 Ld8<T>::store(out + base + e, v);
             } else {
-                out[base + e] = from_f32<T>(g[e] * sc * weight[(size_t)p * part + e]);
+                out[base + e] = from_f32<T>(gp[e] * sc * weight[(size_t)p * part + e]);
             }
         }
-        __syncthreads();                         // g is written again for the next part
+        if (by_warp) __syncwarp();
+        else __syncthreads();                    // g is written again for the next part
     }
     // the portion's last row moves the convolution's window on: its taps - 1 newest inputs
     if (taps > 1 && (t + 1 >= n_rows || token_slot[t + 1] != slot)) {
@@ -220,13 +238,13 @@ using namespace tllm;
 extern "C" {
 
 // conv_w [channels, taps] in the storage type and conv_t, the same taps as [taps, channels] (null: one channel
-// per thread), conv_b [channels] float32 or null; dt_bias, rate (the positive decay rate per head) and skip_d
-// [heads] float32.  tail_off: floats of S before the convolution's window in a request's state.  Outputs
-// float32: qn (C) and kn (B) [n_rows, groups N], vv (dt x) and skip (D x) [n_rows, heads P], decay [n_rows, heads].
+// per thread), conv_b [channels] float32 or null; dt_bias and rate (the positive decay rate per head) [heads]
+// float32.  tail_off: floats of S before the convolution's window in a request's state.  Outputs
+// float32: qn (C) and kn (B) [n_rows, groups N], vv (x) [n_rows, heads P], decay and step (dt) [n_rows, heads].
 int tllm_ssd_prepare(const void* proj, int ld, int dtype, const void* conv_w, const void* conv_t, const float* conv_b, int taps,
-                     const float* dt_bias, const float* rate, const float* skip_d, const int* token_slot,
+                     const float* dt_bias, const float* rate, const int* token_slot,
                      const float* state, long long state_stride, long long tail_off, int heads, int groups, int N,
-                     int P, float* qn, float* kn, float* vv, float* decay, float* skip, int n_rows,
+                     int P, float* qn, float* kn, float* vv, float* decay, float* step, int n_rows,
                      cudaStream_t stream) {
     TLLM_REQUIRE(n_rows >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && N > 0 && P > 0 && taps > 0,
                  "ssd_prepare: bad sizes");
@@ -234,47 +252,58 @@ int tllm_ssd_prepare(const void* proj, int ld, int dtype, const void* conv_w, co
     TLLM_REQUIRE(ld >= inner + channels + heads, "ssd_prepare: rows of %d are too short", ld);
     TLLM_REQUIRE(taps == 1 || state != nullptr, "ssd_prepare: no state for the convolution's window");
     if (n_rows == 0) return 0;
-    const size_t smem = (size_t)heads * sizeof(float);
-    TLLM_REQUIRE(smem <= 48 * 1024, "ssd_prepare: %d heads", heads);
     const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool vec = conv_t != nullptr && P % 8 == 0 && (groups * N) % 8 == 0 && ld % 8 == 0 && tail_off % 4 == 0 &&
                      state_stride % 4 == 0 && al(proj) && al(conv_t) && al(conv_b) && al(state) && al(qn) && al(kn) &&
-                     al(vv) && al(skip);
+                     al(vv);
     const int split = token_split(n_rows, channels / 256 > 0 ? channels / 256 : 1);
-#define PREP(T, V)                                                                                                  \
-    launch_pdl(kPdlOther, ssd_prepare_kernel<T, V>, dim3(n_rows, split), dim3(split > 1 ? 128 : 256), smem, stream, \
-               (const T*)proj, ld, (const T*)(V ? conv_t : conv_w), conv_b, taps, dt_bias, rate, skip_d, token_slot, \
-               state, state_stride, tail_off, heads, groups, N, P, qn, kn, vv, decay, skip)
-    if (dtype == kBF16) { if (vec) PREP(bf16, true); else PREP(bf16, false); }
-    else if (dtype == kF32) { if (vec) PREP(float, true); else PREP(float, false); }
+#define PREP_T(T, V, N)                                                                                             \
+    launch_pdl(kPdlOther, ssd_prepare_kernel<T, V, N>, dim3(n_rows, split), dim3(split > 1 ? 128 : 256), 0, stream, \
+               (const T*)proj, ld, (const T*)(V ? conv_t : conv_w), conv_b, taps, dt_bias, rate, token_slot, \
+               state, state_stride, tail_off, heads, groups, N_state, P, qn, kn, vv, decay, step)
+#define PREP(T)                                                                                                     \
+    do {                                                                                                            \
+        if (!vec) PREP_T(T, false, 0);                                                                              \
+        else if (taps == 2) PREP_T(T, true, 2);                                                                     \
+        else if (taps == 3) PREP_T(T, true, 3);                                                                     \
+        else if (taps == 4) PREP_T(T, true, 4);                                                                     \
+        else PREP_T(T, true, 0);                                                                                    \
+    } while (0)
+    const int N_state = N;
+    if (dtype == kBF16) PREP(bf16);
+    else if (dtype == kF32) PREP(float);
     else TLLM_REQUIRE(false, "ssd_prepare: unknown dtype %d", dtype);
+#undef PREP_T
 #undef PREP
     return finish_launch("ssd_prepare");
 }
 
-// o_raw (the scan's read-out) and skip [n_rows, inner] float32; proj as in ssd_prepare (z in its first `inner`
-// columns, the convolution's inputs behind them); weight [inner] float32; out [n_rows, inner] in the storage type.
-int tllm_ssd_finish(const float* o_raw, const float* skip, const void* proj, int ld, int dtype, const float* weight,
+// o_raw (the scan's read-out) and xs (x after convolution and SiLU) [n_rows, inner] float32; skip_d [inner / P]
+// float32; proj as in ssd_prepare (z in its first `inner` columns, the convolution's inputs behind them); weight
+// [inner] float32; out [n_rows, inner] in the storage type.
+int tllm_ssd_finish(const float* o_raw, const float* xs, const float* skip_d, int P, const void* proj, int ld, int dtype, const float* weight,
                     float eps, int norm_groups, const int* token_slot, int n_rows, int inner, int channels, int taps,
                     float* state, long long state_stride, long long tail_off, void* out, cudaStream_t stream) {
     TLLM_REQUIRE(n_rows >= 0 && inner > 0 && norm_groups > 0 && inner % norm_groups == 0 && eps > 0.0f && taps > 0,
                  "ssd_finish: bad sizes");
     TLLM_REQUIRE(ld >= inner + channels, "ssd_finish: rows of %d are too short", ld);
     if (n_rows == 0) return 0;
+    TLLM_REQUIRE(P > 0 && inner % P == 0, "ssd_finish: heads of %d in rows of %d", P, inner);
     const int part = inner / norm_groups;
-    const size_t smem = (size_t)part * sizeof(float);
+    const int split = token_split(n_rows, norm_groups);
+    const int per_block = (norm_groups + split - 1) / split;
+    const size_t smem = (size_t)part * (per_block >= 8 ? 8 : 1) * sizeof(float);        // a part per warp, or one for the block
     TLLM_REQUIRE(smem <= 200 * 1024, "ssd_finish: parts of %d do not fit in shared memory", part);
     const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-    const bool vec = part % 8 == 0 && ld % 8 == 0 && al(o_raw) && al(skip) && al(proj) && al(weight) && al(out);
-    const int split = token_split(n_rows, norm_groups);
+    const bool vec = part % 8 == 0 && P % 8 == 0 && ld % 8 == 0 && al(o_raw) && al(xs) && al(proj) && al(weight) && al(out);
 #define FIN(T, V)                                                                                                   \
     do {                                                                                                            \
         if (smem > 48 * 1024) {                                                                                     \
             cudaError_t e = cudaFuncSetAttribute(ssd_finish_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) { set_error("ssd_finish: %s", cudaGetErrorString(e)); return (int)e; }            \
         }                                                                                                           \
-        launch_pdl(kPdlOther, ssd_finish_kernel<T, V>, dim3(n_rows, split), dim3(256), smem, stream, o_raw, skip,   \
-                   (const T*)proj, ld, weight, eps, norm_groups, token_slot, n_rows, inner, channels, taps, state,  \
+        launch_pdl(kPdlOther, ssd_finish_kernel<T, V>, dim3(n_rows, split), dim3(256), smem, stream, o_raw, xs,     \
+                   skip_d, P, (const T*)proj, ld, weight, eps, norm_groups, token_slot, n_rows, inner, channels, taps, state,  \
                    state_stride, tail_off, (T*)out);                                                                \
     } while (0)
     if (dtype == kBF16) { if (vec) FIN(bf16, true); else FIN(bf16, false); }

@@ -95,9 +95,9 @@ def _declare(h) -> None:
         "tllm_moe_gather": [vp, vp, vp, i32, vp, i32, i32, vp],
         "tllm_moe_combine": [vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, vp, vp, i32, vp],
         "tllm_sum_rmsnorm": [vp, vp, vp, i32, f32, vp, vp, f32, vp, i32, i32, i32, vp],
-        "tllm_ssd_prepare": [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp,
+        "tllm_ssd_prepare": [vp, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp,
                              vp, vp, i32, vp],
-        "tllm_ssd_finish": [vp, vp, vp, i32, i32, vp, f32, i32, vp, i32, i32, i32, i32, vp, i64, i64, vp, vp],
+        "tllm_ssd_finish": [vp, vp, vp, i32, vp, i32, i32, vp, f32, i32, vp, i32, i32, i32, i32, vp, i64, i64, vp, vp],
         "tllm_gemm_tcgen05_grouped": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp],
         "tllm_add_rmsnorm": [vp, vp, vp, i32, f32, vp, i32, vp, i32, i32, vp],
         "tllm_swiglu": [vp, vp, i32, i32, i32, i32, i32, vp],
@@ -1047,7 +1047,7 @@ def state_space(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch
     assert conv_b is None or (conv_b.dtype == torch.float32 and conv_b.numel() == channels)
     assert out_dtype == proj.dtype and state.shape[1] == state_space_state_floats(heads, groups, n_state, head_dim, taps)
     tail_off = delta_rule_state_floats(heads, groups, n_state, head_dim, 1)
-    ws = workspace(proj.device, tokens * (2 * gn + 3 * inner + heads) + 32)
+    ws = workspace(proj.device, tokens * (2 * gn + 2 * inner + 2 * heads) + 32)
     at = 0
 
     def take(n):
@@ -1055,16 +1055,16 @@ def state_space(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch
         t = ws[at:at + tokens * n]
         at += -(-tokens * n // 4) * 4
         return t
-    qn, kn, decay, vv, o_raw, skipped = take(gn), take(gn), take(heads), take(inner), take(inner), take(inner)
-    _check(lib().tllm_ssd_prepare(_p(proj), ld, _dt(proj), _p(conv_w), _p(conv_t), _p(conv_b), taps, _p(dt_bias), _p(rate), _p(skip),
+    qn, kn, decay, step, vv, o_raw = take(gn), take(gn), take(heads), take(heads), take(inner), take(inner)
+    _check(lib().tllm_ssd_prepare(_p(proj), ld, _dt(proj), _p(conv_w), _p(conv_t), _p(conv_b), taps, _p(dt_bias), _p(rate),
                                   _p(token_slot), _p(state), state.stride(0), tail_off, heads, groups, n_state, head_dim,
-                                  _p(qn), _p(kn), _p(vv), _p(decay), _p(skipped), tokens, _stream()), "ssd_prepare")
+                                  _p(qn), _p(kn), _p(vv), _p(decay), _p(step), tokens, _stream()), "ssd_prepare")
     segments = tokens if seg_info is None else seg_info.shape[0]
     _check(lib().tllm_delta_scan(_p(seg_info), segments, _p(token_slot), _p(qn), _p(kn), _p(vv), None, _p(decay),
                                  _p(state), state.stride(0), heads, groups, n_state, head_dim, _p(o_raw), SCAN_HEAD_DECAY,
-                                 None, 0, 0.0, None, _stream()), "delta_scan")
+                                 _p(step), 0, 0.0, None, _stream()), "delta_scan")
     out = torch.empty((tokens, inner), dtype=out_dtype, device=proj.device)
-    _check(lib().tllm_ssd_finish(_p(o_raw), _p(skipped), _p(proj), ld, _dt(proj), _p(out_weight), float(eps),
+    _check(lib().tllm_ssd_finish(_p(o_raw), _p(vv), _p(skip), head_dim, _p(proj), ld, _dt(proj), _p(out_weight), float(eps),
                                  int(norm_groups), _p(token_slot), tokens, inner, channels, taps, _p(state),
                                  state.stride(0), tail_off, _p(out), _stream()), "ssd_finish")
     return out
